@@ -1,0 +1,152 @@
+/*
+ * palimpsa_b200.h -- C ABI of libpalimpsa_b200.so
+ *
+ * Hand-written sm_100a CUDA implementation of the Palimpsa operator (Bayesian-metaplastic linear
+ * attention): per sequence and head a mean/precision state pair (mu, I) of shape [V, K] is
+ * updated token by token,
+ *
+ *     f_t = exp(-gt_t * g_h)
+ *     M_t = f_t * M_{t-1} + v_t k_t^T                    (M = mu * I)
+ *     I_t = f_t * I_{t-1} + (1 - f_t) * Ip_h + b_t (k_t*k_t)^T
+ *     o_t = scale * (M_t / I_t) q_t          o_var_t = scale * (1 / I_t) (q_t*q_t)
+ *
+ * Every entry point takes a plain struct of device pointers and sizes plus a CUDA stream, enqueues
+ * its kernels on that stream and returns at once: 0 on success, a negative PALIMPSA_E_* code
+ * otherwise.  Nothing here allocates, frees or synchronises unless the comment on the function
+ * says so; the caller owns every buffer.  There is no CPU path.
+ *
+ * Reference interfaces these replace (paths inside the Palimpsa repository):
+ *   palimpsa/ops/palimpsa/chunk_palimpsa_forgetting_scalar.py   chunk_palimpsa, ChunkPalimpsa
+ *   palimpsa/ops/palimpsa/fused_recurrent_palimpsa.py           fused_recurrent_palimpsa
+ *
+ * Tensor layouts (all contiguous, last dimension fastest):
+ *   q, k        [tokens, H, K]   io dtype          v, b, o, o_var, do, do_var   [tokens, H, V]
+ *   gt, dgt     [tokens, H]      float32           g, Ip, dg, dIp               [H] float32
+ *   states      [N, H, V, K]     float32  (V-major, K contiguous: the reference's layout,
+ *                                          chunk_palimpsa_forgetting_scalar.py:475-476)
+ * "tokens" is the flattened (batch, time) axis.  With cu_seqlens == NULL sequence n owns tokens
+ * [n*seq_len, (n+1)*seq_len); otherwise tokens [cu_seqlens[n], cu_seqlens[n+1]).
+ */
+#ifndef PALIMPSA_B200_H
+#define PALIMPSA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PALIMPSA_ABI_VERSION 3
+
+/* io dtype of q, k, v, b, o, o_var, do, do_var, dq, dk, dv, db */
+#define PALIMPSA_F32 0
+#define PALIMPSA_BF16 1
+#define PALIMPSA_F16 2
+
+/* flags */
+#define PALIMPSA_FLAG_UNCERTAINTY 1 /* o_var is produced (forward) / do_var is consumed (backward) */
+#define PALIMPSA_FLAG_EXPLICIT_INIT 2 /* backward only: the forward ran from an explicit initial state
+                                         (init_mu/init_I need not be passed again); changes dIp */
+
+/* error codes */
+#define PALIMPSA_OK 0
+#define PALIMPSA_E_NULL (-1)        /* a required pointer is NULL */
+#define PALIMPSA_E_SHAPE (-2)       /* a size is non-positive or inconsistent */
+#define PALIMPSA_E_DIM (-3)         /* K or V above the supported maximum */
+#define PALIMPSA_E_DTYPE (-4)       /* unknown io dtype */
+#define PALIMPSA_E_WORKSPACE (-5)   /* workspace missing, too small or misaligned */
+#define PALIMPSA_E_LAUNCH (-6)      /* the CUDA runtime refused a launch; see cudaGetLastError */
+#define PALIMPSA_E_ALIGN (-7)       /* a state/workspace pointer is not 16-byte aligned */
+#define PALIMPSA_E_VERSION (-8)     /* struct_size does not match this library */
+#define PALIMPSA_E_LIMIT (-9)       /* problem exceeds a fixed capacity of the entry point */
+
+#define PALIMPSA_MAX_K 256
+#define PALIMPSA_CKPT_INTERVAL 16   /* tokens between saved (M, I) checkpoints */
+
+/* Problem description shared by forward and backward. */
+typedef struct palimpsa_problem {
+    int32_t num_seqs;      /* N: batch size, or number of packed sequences                     */
+    int32_t seq_len;       /* T per sequence when cu_seqlens == NULL (ignored otherwise)       */
+    int32_t total_tokens;  /* rows of q/k/v/b/gt                                               */
+    int32_t H, K, V;
+    int32_t io_dtype;      /* PALIMPSA_F32 / BF16 / F16                                        */
+    int32_t flags;
+    float scale;           /* multiplies q (default of the Python wrappers: K^-0.5)            */
+    int32_t reserved0;
+    const void *q, *k, *v, *b;
+    const float *gt, *g, *Ip;
+    const int32_t *cu_seqlens;    /* [N+1] device, or NULL                                      */
+    const int32_t *chunk_offsets; /* [N] device: first checkpoint slot of each sequence =
+                                     exclusive cumsum of ceil(len/16); NULL => n*ceil(T/16)     */
+    const float *init_mu, *init_I; /* [N,H,V,K] or both NULL (=> mu=0, I=Ip)                     */
+} palimpsa_problem;
+
+/* Forward.  Replaces chunk_palimpsa_fwd_kernel (chunk_palimpsa_forgetting_scalar.py:66-218) and
+ * fused_palimpsa_recurrent_fwd_kernel (fused_recurrent_palimpsa.py:24-154). */
+typedef struct palimpsa_fwd_params {
+    size_t struct_size;    /* sizeof(palimpsa_fwd_params), checked                              */
+    palimpsa_problem p;
+    void *o;               /* [tokens,H,V] io dtype                                             */
+    void *o_var;           /* same, required iff PALIMPSA_FLAG_UNCERTAINTY                      */
+    float *final_mu, *final_I; /* [N,H,V,K] or both NULL; may alias init_mu/init_I (in place)   */
+    float *ckpt_M, *ckpt_I;    /* [slots,H,V,KP] float32 or both NULL.  One (M, I) pair per 16
+                                  tokens of every sequence (state BEFORE the first token of the
+                                  block); needed only by a later backward.  KP = padded K, see
+                                  palimpsa_padded_k().  slots >= palimpsa_ckpt_slots().          */
+} palimpsa_fwd_params;
+
+/* Backward.  Replaces chunk_palimpsa_bwd_kernel (chunk_palimpsa_forgetting_scalar.py:239-434)
+ * and the host-side reductions at :609-613; also serves the fused-recurrent op, whose backward
+ * the reference leaves unimplemented (fused_recurrent_palimpsa.py:250-253). */
+typedef struct palimpsa_bwd_params {
+    size_t struct_size;
+    palimpsa_problem p;
+    const void *d_o;       /* [tokens,H,V] io dtype                                             */
+    const void *d_o_var;   /* required iff PALIMPSA_FLAG_UNCERTAINTY                            */
+    const float *ckpt_M, *ckpt_I; /* written by the forward                                     */
+    void *dq, *dk, *dv, *db;      /* io dtype                                                   */
+    float *dgt;            /* [tokens,H] float32                                                */
+    float *dg, *dIp;       /* [H] float32 (summed over sequences and tokens)                    */
+    void *workspace;       /* scratch, >= palimpsa_bwd_workspace_bytes(), 256-byte aligned       */
+    size_t workspace_bytes;
+} palimpsa_bwd_params;
+
+/* Version of this header the library was built from. */
+int palimpsa_abi_version(void);
+
+/* Human-readable text for a PALIMPSA_E_* code (static storage). */
+const char *palimpsa_last_error_string(int code);
+
+/* K rounded up to the kernels' tile width (16, 32, 48, 64, 96, 128, 192 or 256); 0 if K > 256. */
+int palimpsa_padded_k(int K);
+
+/* Upper bound on checkpoint slots for a problem: ceil(total_tokens/16) + num_seqs (varlen needs
+ * no host synchronisation to size its buffers). */
+long long palimpsa_ckpt_slots(const palimpsa_problem *p);
+
+/* Chunked forward (training / prefill): the layers' mode 'chunk' (palimpsa/layers/palimpsa.py:309). */
+int palimpsa_chunk_fwd(const palimpsa_fwd_params *params, void *cuda_stream);
+
+/* Fused-recurrent forward: the layers' mode 'fused_recurrent' (palimpsa/layers/palimpsa.py:317).
+ * Same kernels as the chunked forward; kept as its own symbol because the reference has two ops. */
+int palimpsa_recurrent_fwd(const palimpsa_fwd_params *params, void *cuda_stream);
+
+/* One decode step for every sequence of a state cache, in place: tokens == num_seqs, seq_len == 1,
+ * final_mu/final_I may equal init_mu/init_I.  The state cache replaces the (final_mu, final_I)
+ * tuple the layer stores in its Cache (palimpsa/layers/palimpsa.py:325-331). */
+int palimpsa_decode_step(const palimpsa_fwd_params *params, void *cuda_stream);
+
+/* Scratch bytes the backward needs for this problem. */
+size_t palimpsa_bwd_workspace_bytes(const palimpsa_problem *p);
+
+/* Backward of the chunked op (ChunkPalimpsa.backward, chunk_palimpsa_forgetting_scalar.py:522-620). */
+int palimpsa_chunk_bwd(const palimpsa_bwd_params *params, void *cuda_stream);
+
+/* Backward of the fused-recurrent op (absent in the reference: fused_recurrent_palimpsa.py:250-253). */
+int palimpsa_recurrent_bwd(const palimpsa_bwd_params *params, void *cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PALIMPSA_B200_H */

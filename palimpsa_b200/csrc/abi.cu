@@ -1,0 +1,137 @@
+// extern "C" surface of libpalimpsa_b200.so: argument validation and dispatch.  No kernel lives
+// here; see fwd.cu and bwd.cu.
+#include "common.cuh"
+#include "host.h"
+
+using namespace palimpsa;
+
+namespace {
+
+int check_problem(const palimpsa_problem& p) {
+    if (p.num_seqs <= 0 || p.H <= 0 || p.K <= 0 || p.V <= 0 || p.total_tokens < 0) return PALIMPSA_E_SHAPE;
+    if (!p.cu_seqlens && (p.seq_len < 0 || (long long)p.seq_len * p.num_seqs != p.total_tokens))
+        return PALIMPSA_E_SHAPE;
+    if (p.K > PALIMPSA_MAX_K) return PALIMPSA_E_DIM;
+    if (p.io_dtype != PALIMPSA_F32 && p.io_dtype != PALIMPSA_BF16 && p.io_dtype != PALIMPSA_F16)
+        return PALIMPSA_E_DTYPE;
+    if (!p.g || !p.Ip) return PALIMPSA_E_NULL;
+    if (p.total_tokens > 0 && (!p.q || !p.k || !p.v || !p.b || !p.gt)) return PALIMPSA_E_NULL;
+    if ((p.init_mu == nullptr) != (p.init_I == nullptr)) return PALIMPSA_E_NULL;
+    if ((long long)p.total_tokens * p.H >= (1ll << 31)) return PALIMPSA_E_SHAPE;
+    return PALIMPSA_OK;
+}
+
+bool misaligned16(const void* x) { return x && (reinterpret_cast<uintptr_t>(x) & 15); }
+
+int check_fwd(const palimpsa_fwd_params* prm) {
+    if (!prm) return PALIMPSA_E_NULL;
+    if (prm->struct_size != sizeof(palimpsa_fwd_params)) return PALIMPSA_E_VERSION;
+    int rc = check_problem(prm->p);
+    if (rc) return rc;
+    const palimpsa_problem& p = prm->p;
+    if (p.total_tokens > 0 && !prm->o) return PALIMPSA_E_NULL;
+    if ((p.flags & PALIMPSA_FLAG_UNCERTAINTY) && p.total_tokens > 0 && !prm->o_var) return PALIMPSA_E_NULL;
+    if ((prm->final_mu == nullptr) != (prm->final_I == nullptr)) return PALIMPSA_E_NULL;
+    if ((prm->ckpt_M == nullptr) != (prm->ckpt_I == nullptr)) return PALIMPSA_E_NULL;
+    if (misaligned16(prm->ckpt_M) || misaligned16(prm->ckpt_I)) return PALIMPSA_E_ALIGN;
+    if (p.K % 4 == 0 && (misaligned16(p.init_mu) || misaligned16(p.init_I) || misaligned16(prm->final_mu) ||
+                         misaligned16(prm->final_I)))
+        return PALIMPSA_E_ALIGN;
+    return PALIMPSA_OK;
+}
+
+int check_bwd(const palimpsa_bwd_params* prm) {
+    if (!prm) return PALIMPSA_E_NULL;
+    if (prm->struct_size != sizeof(palimpsa_bwd_params)) return PALIMPSA_E_VERSION;
+    int rc = check_problem(prm->p);
+    if (rc) return rc;
+    const palimpsa_problem& p = prm->p;
+    if (!prm->dg || !prm->dIp) return PALIMPSA_E_NULL;
+    if (p.total_tokens > 0) {
+        if (!prm->d_o || !prm->ckpt_M || !prm->ckpt_I || !prm->dq || !prm->dk || !prm->dv || !prm->db || !prm->dgt)
+            return PALIMPSA_E_NULL;
+        if ((p.flags & PALIMPSA_FLAG_UNCERTAINTY) && !prm->d_o_var) return PALIMPSA_E_NULL;
+    }
+    if (misaligned16(prm->ckpt_M) || misaligned16(prm->ckpt_I)) return PALIMPSA_E_ALIGN;
+    const size_t need = palimpsa_bwd_workspace_bytes(&p);
+    if (need == 0) return PALIMPSA_E_DIM;
+    if (!prm->workspace || prm->workspace_bytes < need) return PALIMPSA_E_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(prm->workspace) & 255) return PALIMPSA_E_WORKSPACE;
+    return PALIMPSA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int palimpsa_abi_version(void) { return PALIMPSA_ABI_VERSION; }
+
+const char* palimpsa_last_error_string(int code) {
+    switch (code) {
+        case PALIMPSA_OK: return "ok";
+        case PALIMPSA_E_NULL: return "a required pointer is NULL (or only one of a pointer pair was given)";
+        case PALIMPSA_E_SHAPE: return "a size is non-positive or inconsistent";
+        case PALIMPSA_E_DIM: return "d_k above the supported maximum for this entry point";
+        case PALIMPSA_E_DTYPE: return "unknown io dtype";
+        case PALIMPSA_E_WORKSPACE: return "workspace missing, too small or not 256-byte aligned";
+        case PALIMPSA_E_LAUNCH: return "the CUDA runtime refused a kernel launch";
+        case PALIMPSA_E_ALIGN: return "a state or checkpoint pointer is not 16-byte aligned";
+        case PALIMPSA_E_VERSION: return "struct_size does not match this library (header/library mismatch)";
+        case PALIMPSA_E_LIMIT: return "problem exceeds a fixed capacity of this entry point";
+        default: return "unknown error code";
+    }
+}
+
+int palimpsa_padded_k(int K) {
+    static const int sizes[] = {16, 32, 48, 64, 96, 128, 192, 256};
+    if (K <= 0) return 0;
+    for (int s : sizes)
+        if (K <= s) return s;
+    return 0;
+}
+
+long long palimpsa_ckpt_slots(const palimpsa_problem* p) {
+    if (!p) return 0;
+    return ((long long)p->total_tokens + TB - 1) / TB + p->num_seqs;
+}
+
+int palimpsa_chunk_fwd(const palimpsa_fwd_params* prm, void* cuda_stream) {
+    int rc = check_fwd(prm);
+    if (rc) return rc;
+    return launch_fwd(prm, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int palimpsa_recurrent_fwd(const palimpsa_fwd_params* prm, void* cuda_stream) {
+    int rc = check_fwd(prm);
+    if (rc) return rc;
+    return launch_fwd(prm, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int palimpsa_decode_step(const palimpsa_fwd_params* prm, void* cuda_stream) {
+    int rc = check_fwd(prm);
+    if (rc) return rc;
+    const palimpsa_problem& p = prm->p;
+    if (p.cu_seqlens || p.seq_len != 1 || p.total_tokens != p.num_seqs) return PALIMPSA_E_SHAPE;
+    if (!p.init_mu || !prm->final_mu) return PALIMPSA_E_NULL;
+    if (prm->ckpt_M) return PALIMPSA_E_SHAPE;
+    return launch_fwd(prm, static_cast<cudaStream_t>(cuda_stream));
+}
+
+size_t palimpsa_bwd_workspace_bytes(const palimpsa_problem* p) {
+    if (!p || p->K <= 0 || p->V <= 0 || p->K > PALIMPSA_MAX_K) return 0;
+    return bwd_workspace_layout(*p).total;
+}
+
+int palimpsa_chunk_bwd(const palimpsa_bwd_params* prm, void* cuda_stream) {
+    int rc = check_bwd(prm);
+    if (rc) return rc;
+    return launch_bwd(prm, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int palimpsa_recurrent_bwd(const palimpsa_bwd_params* prm, void* cuda_stream) {
+    int rc = check_bwd(prm);
+    if (rc) return rc;
+    return launch_bwd(prm, static_cast<cudaStream_t>(cuda_stream));
+}
+
+}  // extern "C"

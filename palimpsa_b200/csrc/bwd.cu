@@ -1,0 +1,731 @@
+// Backward kernels of the Palimpsa operator (sm_100a).
+//
+// Main kernel: one CTA owns TV state rows x all KP columns of one (sequence, head) and walks the
+// sequence's 16-token blocks from the last to the first.  Per block it
+//   1. takes the block's start state (M, I) from the checkpoint the forward saved (prefetched into
+//      shared memory one block ahead with cp.async, together with the block's raw inputs),
+//   2. sweeps forward once, parking the state at the start of each 4-token group (thread-private
+//      slots in shared memory),
+//   3. per group, last first: recomputes the 4 per-token states into registers, then walks the
+//      tokens in reverse, carrying the state gradients (GM, -GI) in registers:
+//          h    = dy*q_s / I            GM = f_next*GM + h          -GI = f_next*(-GI) + h*mu (+var)
+//          dq  += dy*mu   dk += GM*v + 2k*GI*b   dv += GM*k   db += GI*k^2
+//          df   = <GM, M_prev> + <GI, I_prev - Ip>
+//      (the algebra of chunk_palimpsa_bwd_kernel, chunk_palimpsa_forgetting_scalar.py:343-434,
+//      with the previous state carried forward instead of rebuilt by a division, :409-410).
+// Reductions: over d_k (dv, db) by xor-shuffles inside the lanes of a row; over d_v (dq, dk) first
+// in registers across a thread's rows, then across the CTA's row groups through shared memory, and
+// across the CTAs of different row tiles through fp32 partial buffers in the workspace, which the
+// finishing kernel sums in a fixed order (bitwise reproducible; no atomics).
+//
+// Finishing kernels: (1) per (token, head) row: sum the row tiles, cast dq/dk, form
+// dgt = -g f df and the per-row terms of dg and dIp; (2) per head: ordered sum over rows.
+#include "common.cuh"
+#include "host.h"
+
+namespace palimpsa {
+
+constexpr int GR = 4;  // tokens per register-resident group
+
+struct BwdArgs {
+    palimpsa_problem p;
+    const void* d_o;
+    const void* d_o_var;
+    const float* ckpt_M;
+    const float* ckpt_I;
+    float *dq_part, *dk_part, *df_part, *dip_part;
+    void *dv, *db;
+    int aligned;
+    int rows_total;  // tokens * H
+};
+
+struct BwdSmem {
+    int ks, qs, qqs, vs, bs, dys, dyvs, fcn, dvs, dbs, wred, slots, ckb, kred;
+    int ck_stage;  // bytes of one (M, I) checkpoint stage
+    int raw, rq, rk, rv, rb, rdo, rdov, rgt, raw_stage;
+    int total;
+};
+
+__host__ __device__ inline BwdSmem bwd_smem_layout(int KP, int TV, int NE, int nthr, int WV, int es, bool unc) {
+    BwdSmem s;
+    int off = 0;
+    auto take = [&](int bytes) {
+        int o = off;
+        off += round_up(bytes, 16);
+        return o;
+    };
+    s.ks = take(TB * KP * 4);
+    s.qs = take(TB * KP * 4);
+    s.qqs = unc ? take(TB * KP * 4) : 0;
+    s.vs = take(TB * TV * 4);
+    s.bs = take(TB * TV * 4);
+    s.dys = take(TB * TV * 4);
+    s.dyvs = unc ? take(TB * TV * 4) : 0;
+    s.fcn = take(TB * 16);
+    s.dvs = take(TB * TV * 4);
+    s.dbs = take(TB * TV * 4);
+    s.wred = take((nthr / 32) * TB * 2 * 4);
+    s.slots = take(2 * 2 * NE * nthr * 4);
+    s.ck_stage = 2 * TV * KP * 4;
+    s.ckb = take(2 * s.ck_stage);
+    s.kred = take(GR * WV * (unc ? 4 : 3) * KP * 4);
+    s.raw = off;
+    int r = 0;
+    auto rtake = [&](int bytes) {
+        int o = r;
+        r += round_up(bytes, 16);
+        return o;
+    };
+    s.rq = rtake(TB * KP * es);
+    s.rk = rtake(TB * KP * es);
+    s.rv = rtake(TB * TV * es);
+    s.rb = rtake(TB * TV * es);
+    s.rdo = rtake(TB * TV * es);
+    s.rdov = unc ? rtake(TB * TV * es) : 0;
+    s.rgt = rtake((TB + 1) * 4);
+    s.raw_stage = r;
+    s.total = off + 2 * r;
+    return s;
+}
+
+// Asynchronous copies for one block: checkpoint rows always, raw inputs on the aligned path.
+__device__ __forceinline__ void bwd_issue(const BwdArgs& a, unsigned char* sm, const BwdSmem& L, int stage_idx, int es,
+                                          int KP, int TV, long long tok0, int nt, int nt_ext, long long slot, int h,
+                                          int v0, int tvw) {
+    const palimpsa_problem& p = a.p;
+    const int nthr = blockDim.x, tid = threadIdx.x;
+    // checkpoint (M, I): tvw rows of KP floats
+    {
+        unsigned char* ck = sm + L.ckb + stage_idx * L.ck_stage;
+        const int cr = KP / 4;
+        const long long base = ((slot * p.H + h) * (long long)p.V + v0) * KP;
+        for (int i = tid; i < tvw * cr; i += nthr) {
+            cp_async16(ck + i * 16, a.ckpt_M + base + (long long)i * 4);
+            cp_async16(ck + TV * KP * 4 + i * 16, a.ckpt_I + base + (long long)i * 4);
+        }
+    }
+    if (!a.aligned) return;
+    unsigned char* stage = sm + L.raw + stage_idx * L.raw_stage;
+    const int cq = p.K * es / 16;
+    const char* gq = reinterpret_cast<const char*>(p.q);
+    const char* gk = reinterpret_cast<const char*>(p.k);
+    for (int i = tid; i < nt * cq; i += nthr) {
+        int t = i / cq, c = i - t * cq;
+        long long src = ((tok0 + t) * p.H + h) * (long long)p.K * es + c * 16;
+        int dst = t * KP * es + c * 16;
+        cp_async16(stage + L.rq + dst, gq + src);
+        cp_async16(stage + L.rk + dst, gk + src);
+    }
+    const int cv = tvw * es / 16;
+    const char* gv = reinterpret_cast<const char*>(p.v);
+    const char* gb = reinterpret_cast<const char*>(p.b);
+    const char* gdo = reinterpret_cast<const char*>(a.d_o);
+    const char* gdov = reinterpret_cast<const char*>(a.d_o_var);
+    for (int i = tid; i < nt * cv; i += nthr) {
+        int t = i / cv, c = i - t * cv;
+        long long src = (((tok0 + t) * p.H + h) * (long long)p.V + v0) * es + c * 16;
+        int dst = t * TV * es + c * 16;
+        cp_async16(stage + L.rv + dst, gv + src);
+        cp_async16(stage + L.rb + dst, gb + src);
+        cp_async16(stage + L.rdo + dst, gdo + src);
+        if (gdov) cp_async16(stage + L.rdov + dst, gdov + src);
+    }
+    for (int i = tid; i < nt_ext; i += nthr) cp_async4(stage + L.rgt + i * 4, p.gt + (tok0 + i) * p.H + h);
+}
+
+template <int DT, bool ALIGNED, bool UNC>
+__device__ __forceinline__ void bwd_convert(const BwdArgs& a, unsigned char* sm, const unsigned char* stage,
+                                            const BwdSmem& L, int KP, int TV, long long tok0, int nt, int nt_ext,
+                                            int h, int v0, float gh, float iph) {
+    const palimpsa_problem& p = a.p;
+    const int nthr = blockDim.x, tid = threadIdx.x;
+    const int K4 = KP / 4, V4 = TV / 4;
+    float4* qs = reinterpret_cast<float4*>(sm + L.qs);
+    float4* ks = reinterpret_cast<float4*>(sm + L.ks);
+    float4* qqs = reinterpret_cast<float4*>(sm + L.qqs);
+    const float sc = p.scale;
+    for (int i = tid; i < TB * K4; i += nthr) {
+        int t = i / K4, c4 = i - t * K4;
+        float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), kv = qv;
+        if (t < nt && c4 * 4 < p.K) {
+            if (ALIGNED) {
+                qv = ld4<DT>(stage + L.rq, i);
+                kv = ld4<DT>(stage + L.rk, i);
+            } else {
+                long long row = ((tok0 + t) * p.H + h) * (long long)p.K;
+                qv = ld4_guarded<DT>(p.q, row + c4 * 4, row + p.K);
+                kv = ld4_guarded<DT>(p.k, row + c4 * 4, row + p.K);
+            }
+        }
+        qs[i] = make_float4(qv.x * sc, qv.y * sc, qv.z * sc, qv.w * sc);
+        ks[i] = kv;
+        if (UNC) qqs[i] = make_float4(sc * qv.x * qv.x, sc * qv.y * qv.y, sc * qv.z * qv.z, sc * qv.w * qv.w);
+    }
+    float4* vs = reinterpret_cast<float4*>(sm + L.vs);
+    float4* bs = reinterpret_cast<float4*>(sm + L.bs);
+    float4* dys = reinterpret_cast<float4*>(sm + L.dys);
+    float4* dyvs = reinterpret_cast<float4*>(sm + L.dyvs);
+    for (int i = tid; i < TB * V4; i += nthr) {
+        int t = i / V4, c4 = i - t * V4;
+        float4 vv = make_float4(0.f, 0.f, 0.f, 0.f), bv = vv, dv = vv, dvv = vv;
+        if (t < nt && v0 + c4 * 4 < p.V) {
+            if (ALIGNED) {
+                vv = ld4<DT>(stage + L.rv, i);
+                bv = ld4<DT>(stage + L.rb, i);
+                dv = ld4<DT>(stage + L.rdo, i);
+                if (UNC) dvv = ld4<DT>(stage + L.rdov, i);
+            } else {
+                long long row = ((tok0 + t) * p.H + h) * (long long)p.V;
+                vv = ld4_guarded<DT>(p.v, row + v0 + c4 * 4, row + p.V);
+                bv = ld4_guarded<DT>(p.b, row + v0 + c4 * 4, row + p.V);
+                dv = ld4_guarded<DT>(a.d_o, row + v0 + c4 * 4, row + p.V);
+                if (UNC) dvv = ld4_guarded<DT>(a.d_o_var, row + v0 + c4 * 4, row + p.V);
+            }
+        }
+        vs[i] = vv;
+        bs[i] = bv;
+        dys[i] = dv;
+        if (UNC) dyvs[i] = dvv;
+    }
+    // per token: f, c = (1-f)*Ip, f of the NEXT token of the sequence (0 past its end), gt
+    float4* fcn = reinterpret_cast<float4*>(sm + L.fcn);
+    for (int i = tid; i < TB; i += nthr) {
+        float g0 = 0.f, g1 = 0.f;
+        const bool has0 = i < nt, has1 = i + 1 < nt_ext;
+        if (ALIGNED) {
+            const float* rg = reinterpret_cast<const float*>(stage + L.rgt);
+            if (has0) g0 = rg[i];
+            if (has1) g1 = rg[i + 1];
+        } else {
+            if (has0) g0 = p.gt[(tok0 + i) * p.H + h];
+            if (has1) g1 = p.gt[(tok0 + i + 1) * p.H + h];
+        }
+        const float f = expf(-g0 * gh);
+        const float fn = has1 ? expf(-g1 * gh) : 0.f;
+        fcn[i] = make_float4(f, (1.f - f) * iph, fn, g0);
+    }
+}
+
+template <int RV, int NP>
+struct State {
+    float2 M[RV][NP], I[RV][NP];
+};
+
+template <int RK, int KG, int RV, bool UNC>
+__global__ void __launch_bounds__(256) bwd_kernel(const BwdArgs a) {
+    constexpr int KP = RK * KG, VG = 32 / KG, NP = RK / 2, NE = RV * RK, NQ = UNC ? 4 : 3, KP2 = KP / 2;
+    extern __shared__ __align__(16) unsigned char sm[];
+    const palimpsa_problem& p = a.p;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, nthr = blockDim.x, W = nthr >> 5;
+    const int TV = W * VG * RV, WV = W * VG;
+    const int kg = lane % KG, vg = lane / KG, wv = w * VG + vg;
+    const int row0 = wv * RV;
+    const int n = blockIdx.y / p.H, h = blockIdx.y - n * p.H;
+    const int tile = blockIdx.x;
+    const int v0 = tile * TV;
+    const int tvw = min(TV, p.V - v0);
+    const int es = dtype_size(p.io_dtype);
+    const BwdSmem L = bwd_smem_layout(KP, TV, NE, nthr, WV, es, UNC);
+    int bos, len;
+    seq_range(p, n, bos, len);
+    if (len <= 0) return;
+    const float gh = p.g[h], iph = p.Ip[h];
+    const int V = p.V;
+    const long long slot0 = seq_first_slot(p, n);
+    const int nblk = (len + TB - 1) / TB;
+    const bool has_init = p.init_mu != nullptr || (p.flags & PALIMPSA_FLAG_EXPLICIT_INIT);
+
+    const float2* ks2 = reinterpret_cast<const float2*>(sm + L.ks);
+    const float2* qs2 = reinterpret_cast<const float2*>(sm + L.qs);
+    const float2* qqs2 = reinterpret_cast<const float2*>(sm + L.qqs);
+    const float* vs = reinterpret_cast<const float*>(sm + L.vs);
+    const float* bs = reinterpret_cast<const float*>(sm + L.bs);
+    const float* dys = reinterpret_cast<const float*>(sm + L.dys);
+    const float* dyvs = reinterpret_cast<const float*>(sm + L.dyvs);
+    const float4* fcn = reinterpret_cast<const float4*>(sm + L.fcn);
+    float* dvs = reinterpret_cast<float*>(sm + L.dvs);
+    float* dbs = reinterpret_cast<float*>(sm + L.dbs);
+    float* wred = reinterpret_cast<float*>(sm + L.wred);
+    float* slots = reinterpret_cast<float*>(sm + L.slots);
+    float2* kred2 = reinterpret_cast<float2*>(sm + L.kred);
+
+    // running state gradients: GM = dL/dM_t, nGI = -dL/dI_t of the earliest token processed so far
+    float2 GM[RV][NP], nGI[RV][NP];
+#pragma unroll
+    for (int r = 0; r < RV; ++r)
+#pragma unroll
+        for (int q = 0; q < NP; ++q) GM[r][q] = nGI[r][q] = make_float2(0.f, 0.f);
+
+    auto load_ck = [&](State<RV, NP>& s, int stage_idx) {
+        const float* ckM = reinterpret_cast<const float*>(sm + L.ckb + stage_idx * L.ck_stage);
+        const float* ckI = ckM + TV * KP;
+#pragma unroll
+        for (int r = 0; r < RV; ++r) {
+            const bool ok = row0 + r < tvw;
+#pragma unroll
+            for (int q = 0; q < NP; ++q) {
+                const int e = (row0 + r) * KP + 2 * (q * KG + kg);
+                s.M[r][q] = ok ? *reinterpret_cast<const float2*>(ckM + e) : make_float2(0.f, 0.f);
+                s.I[r][q] = ok ? *reinterpret_cast<const float2*>(ckI + e) : make_float2(1.f, 1.f);
+            }
+        }
+    };
+    // one forward step of the recurrence on token tl of the staged block
+    auto fstep = [&](State<RV, NP>& s, int tl) {
+        const float4 fv = fcn[tl];
+        const float2 ff = dup2(fv.x), cc = dup2(fv.y);
+        float2 vr[RV], br[RV];
+#pragma unroll
+        for (int r = 0; r < RV; ++r) {
+            vr[r] = dup2(vs[tl * TV + row0 + r]);
+            br[r] = dup2(bs[tl * TV + row0 + r]);
+        }
+#pragma unroll
+        for (int q = 0; q < NP; ++q) {
+            const float2 kp = ks2[tl * KP2 + q * KG + kg];
+            const float2 kk = fmul2(kp, kp);
+#pragma unroll
+            for (int r = 0; r < RV; ++r) {
+                s.M[r][q] = ffma2(ff, s.M[r][q], fmul2(vr[r], kp));
+                s.I[r][q] = ffma2(ff, s.I[r][q], ffma2(br[r], kk, cc));
+            }
+        }
+    };
+
+    {
+        const int c = nblk - 1;
+        const int nt = min(TB, len - c * TB);
+        bwd_issue(a, sm, L, 0, es, KP, TV, (long long)bos + c * TB, nt, min(TB + 1, len - c * TB), slot0 + c, h, v0,
+                  tvw);
+        cp_async_commit();
+    }
+
+    for (int it = 0; it < nblk; ++it) {
+        const int c = nblk - 1 - it;
+        const int t0 = c * TB;
+        const int nt = min(TB, len - t0);
+        const int nt_ext = min(TB + 1, len - t0);
+        const long long tok0 = (long long)bos + t0;
+        const int st = it & 1;
+        if (c > 0) {
+            const int t0n = t0 - TB;
+            bwd_issue(a, sm, L, st ^ 1, es, KP, TV, (long long)bos + t0n, TB, min(TB + 1, len - t0n), slot0 + c - 1, h,
+                      v0, tvw);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        {
+            const unsigned char* stage = sm + L.raw + st * L.raw_stage;
+            if (a.aligned) {
+                if (p.io_dtype == PALIMPSA_BF16)
+                    bwd_convert<PALIMPSA_BF16, true, UNC>(a, sm, stage, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
+                else if (p.io_dtype == PALIMPSA_F32)
+                    bwd_convert<PALIMPSA_F32, true, UNC>(a, sm, stage, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
+                else
+                    bwd_convert<PALIMPSA_F16, true, UNC>(a, sm, stage, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
+            } else {
+                if (p.io_dtype == PALIMPSA_BF16)
+                    bwd_convert<PALIMPSA_BF16, false, UNC>(a, sm, stage, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
+                else if (p.io_dtype == PALIMPSA_F32)
+                    bwd_convert<PALIMPSA_F32, false, UNC>(a, sm, stage, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
+                else
+                    bwd_convert<PALIMPSA_F16, false, UNC>(a, sm, stage, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
+            }
+        }
+        __syncthreads();
+
+        // ---- forward sweep: park the start state of groups 1 .. glast-1, keep glast's in registers
+        const int glast = (nt - 1) / GR;
+        State<RV, NP> P[GR + 1];
+        load_ck(P[0], st);
+        for (int t = 0; t < glast * GR; ++t) {
+            fstep(P[0], t);
+            if ((t & (GR - 1)) == GR - 1 && (t / GR) + 1 < glast) {
+                float* sl = slots + (size_t)(t / GR) * 2 * NE * nthr;
+#pragma unroll
+                for (int r = 0; r < RV; ++r)
+#pragma unroll
+                    for (int q = 0; q < NP; ++q) {
+                        const int e = (r * NP + q) * 4;
+                        sl[(e + 0) * nthr + tid] = P[0].M[r][q].x;
+                        sl[(e + 1) * nthr + tid] = P[0].M[r][q].y;
+                        sl[(e + 2) * nthr + tid] = P[0].I[r][q].x;
+                        sl[(e + 3) * nthr + tid] = P[0].I[r][q].y;
+                    }
+            }
+        }
+
+        for (int gi = glast; gi >= 0; --gi) {
+            if (gi < glast) {
+                if (gi == 0) {
+                    load_ck(P[0], st);
+                } else {
+                    const float* sl = slots + (size_t)(gi - 1) * 2 * NE * nthr;
+#pragma unroll
+                    for (int r = 0; r < RV; ++r)
+#pragma unroll
+                        for (int q = 0; q < NP; ++q) {
+                            const int e = (r * NP + q) * 4;
+                            P[0].M[r][q] = make_float2(sl[(e + 0) * nthr + tid], sl[(e + 1) * nthr + tid]);
+                            P[0].I[r][q] = make_float2(sl[(e + 2) * nthr + tid], sl[(e + 3) * nthr + tid]);
+                        }
+                }
+            }
+            const int ng = min(GR, nt - gi * GR);
+#pragma unroll
+            for (int j = 0; j < GR; ++j) {
+                if (j < ng) {
+                    P[j + 1] = P[j];
+                    fstep(P[j + 1], gi * GR + j);
+                }
+            }
+            // ---- reverse walk over the group ----------------------------------------------------
+#pragma unroll
+            for (int j = GR - 1; j >= 0; --j) {
+                if (j < ng) {
+                    const int tl = gi * GR + j;
+                    const float4 fv = fcn[tl];
+                    const float2 fn = dup2(fv.z);
+                    float2 dqs[NP], Ak[NP], Bk[NP], Uk[NP];
+                    float2 Sa = make_float2(0.f, 0.f), Sb = Sa, Sc = Sa;
+#pragma unroll
+                    for (int q = 0; q < NP; ++q) dqs[q] = Ak[q] = Bk[q] = Uk[q] = make_float2(0.f, 0.f);
+                    float dvr[RV], dbr[RV];
+                    float2 kp[NP], kk[NP], qp[NP], qq[NP];
+#pragma unroll
+                    for (int q = 0; q < NP; ++q) {
+                        kp[q] = ks2[tl * KP2 + q * KG + kg];
+                        kk[q] = fmul2(kp[q], kp[q]);
+                        qp[q] = qs2[tl * KP2 + q * KG + kg];
+                        qq[q] = UNC ? qqs2[tl * KP2 + q * KG + kg] : make_float2(0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int r = 0; r < RV; ++r) {
+                        const float2 vv = dup2(vs[tl * TV + row0 + r]);
+                        const float2 bv = dup2(bs[tl * TV + row0 + r]);
+                        const float2 dy = dup2(dys[tl * TV + row0 + r]);
+                        const float2 dyv = UNC ? dup2(dyvs[tl * TV + row0 + r]) : make_float2(0.f, 0.f);
+                        float2 dva = make_float2(0.f, 0.f), dba = dva;
+#pragma unroll
+                        for (int q = 0; q < NP; ++q) {
+                            const float2 Mt = P[j + 1].M[r][q], It = P[j + 1].I[r][q];
+                            const float2 rr = rcp2(It);
+                            const float2 mu = fmul2(Mt, rr);
+                            const float2 hh = fmul2(fmul2(dy, qp[q]), rr);
+                            GM[r][q] = ffma2(fn, GM[r][q], hh);
+                            float2 hm = fmul2(hh, mu);
+                            if (UNC) hm = ffma2(fmul2(dyv, qq[q]), fmul2(rr, rr), hm);
+                            nGI[r][q] = ffma2(fn, nGI[r][q], hm);
+                            dqs[q] = ffma2(dy, mu, dqs[q]);
+                            if (UNC) Uk[q] = ffma2(dyv, rr, Uk[q]);
+                            Ak[q] = ffma2(GM[r][q], vv, Ak[q]);
+                            Bk[q] = ffma2(nGI[r][q], bv, Bk[q]);
+                            dva = ffma2(GM[r][q], kp[q], dva);
+                            dba = ffma2(nGI[r][q], kk[q], dba);
+                            Sa = ffma2(GM[r][q], P[j].M[r][q], Sa);
+                            Sb = ffma2(nGI[r][q], P[j].I[r][q], Sb);
+                            Sc = fadd2(Sc, nGI[r][q]);
+                        }
+                        dvr[r] = dva.x + dva.y;
+                        dbr[r] = dba.x + dba.y;
+                    }
+                    // d_k-indexed partial sums of this thread's rows -> shared memory
+                    {
+                        float2* dst = kred2 + ((size_t)(j * WV + wv) * NQ) * KP2;
+#pragma unroll
+                        for (int q = 0; q < NP; ++q) {
+                            const int pi = q * KG + kg;
+                            dst[0 * KP2 + pi] = dqs[q];
+                            dst[1 * KP2 + pi] = Ak[q];
+                            dst[2 * KP2 + pi] = Bk[q];
+                            if (UNC) dst[3 * KP2 + pi] = Uk[q];
+                        }
+                    }
+                    // d_v-indexed sums: reduce over the KG lanes of the row
+#pragma unroll
+                    for (int r = 0; r < RV; ++r) {
+                        float x = dvr[r], y = dbr[r];
+#pragma unroll
+                        for (int off = KG / 2; off >= 1; off >>= 1) {
+                            x += __shfl_xor_sync(0xffffffffu, x, off);
+                            y += __shfl_xor_sync(0xffffffffu, y, off);
+                        }
+                        if (kg == 0) {
+                            dvs[tl * TV + row0 + r] = x;
+                            dbs[tl * TV + row0 + r] = -y;
+                        }
+                    }
+                    // decay gradient and sum of GI: reduce over the warp
+                    {
+                        const float sc_ = Sc.x + Sc.y;
+                        float x = (Sa.x + Sa.y) - (Sb.x + Sb.y) + iph * sc_;
+                        float y = -sc_;
+#pragma unroll
+                        for (int off = 16; off >= 1; off >>= 1) {
+                            x += __shfl_xor_sync(0xffffffffu, x, off);
+                            y += __shfl_xor_sync(0xffffffffu, y, off);
+                        }
+                        if (lane == 0) {
+                            wred[(w * TB + tl) * 2 + 0] = x;
+                            wred[(w * TB + tl) * 2 + 1] = y;
+                        }
+                    }
+                }
+            }
+            __syncthreads();
+            // ---- sum the row groups' d_k-indexed partials; emit this row tile's dq / dk --------------
+            for (int i = tid; i < ng * KP2; i += nthr) {
+                const int j = i / KP2, pi = i - j * KP2;
+                const int tl = gi * GR + j;
+                float2 s0 = make_float2(0.f, 0.f), s1 = s0, s2 = s0, s3 = s0;
+                for (int x = 0; x < WV; ++x) {
+                    const float2* src = kred2 + ((size_t)(j * WV + x) * NQ) * KP2 + pi;
+                    s0 = fadd2(s0, src[0]);
+                    s1 = fadd2(s1, src[KP2]);
+                    s2 = fadd2(s2, src[2 * KP2]);
+                    if (UNC) s3 = fadd2(s3, src[3 * KP2]);
+                }
+                const float2 kv = ks2[tl * KP2 + pi];
+                float2 dqv = make_float2(p.scale * s0.x, p.scale * s0.y);
+                if (UNC) {
+                    const float2 qv = qs2[tl * KP2 + pi];
+                    dqv.x += 2.f * qv.x * s3.x;
+                    dqv.y += 2.f * qv.y * s3.y;
+                }
+                const float2 dkv = make_float2(s1.x - 2.f * kv.x * s2.x, s1.y - 2.f * kv.y * s2.y);
+                const size_t e = (((size_t)tile * a.rows_total + (size_t)(tok0 + tl) * p.H + h) * KP2) + pi;
+                reinterpret_cast<float2*>(a.dq_part)[e] = dqv;
+                reinterpret_cast<float2*>(a.dk_part)[e] = dkv;
+            }
+            __syncthreads();
+        }
+
+        // ---- block epilogue: dv, db rows and the per-token scalars -----------------------------------
+        for (int i = tid; i < nt * TV; i += nthr) {
+            const int t = i / TV, r = i - t * TV;
+            if (r < tvw) {
+                const long long e = ((tok0 + t) * p.H + h) * (long long)V + v0 + r;
+                st1(a.dv, e, dvs[i], p.io_dtype);
+                st1(a.db, e, dbs[i], p.io_dtype);
+            }
+        }
+        if (tid < nt) {
+            float df = 0.f, s2 = 0.f;
+            for (int x = 0; x < W; ++x) {
+                df += wred[(x * TB + tid) * 2 + 0];
+                s2 += wred[(x * TB + tid) * 2 + 1];
+            }
+            const float f = fcn[tid].x;
+            float dip = (1.f - f) * s2;
+            if (t0 + tid == 0 && !has_init) dip += f * s2;  // I_0 = Ip: the start-state gradient reaches Ip
+            const size_t e = (size_t)tile * a.rows_total + (size_t)(tok0 + tid) * p.H + h;
+            a.df_part[e] = df;
+            a.dip_part[e] = dip;
+        }
+        // the next iteration's first barrier orders these reads before the buffers are reused
+    }
+}
+
+// ---- finishing kernel 1: one warp per (token, head) row ------------------------------------------------
+__global__ void bwd_finish_rows(const palimpsa_problem p, const float* __restrict__ dq_part,
+                                const float* __restrict__ dk_part, const float* __restrict__ df_part,
+                                const float* __restrict__ dip_part, void* dq, void* dk, float* dgt, float* w_dg,
+                                float* w_dip, int tiles, int KP, long long rows) {
+    const int lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int h = (int)(row % p.H);
+    const int KP2 = KP / 2;
+    for (int pi = lane; pi < KP2; pi += 32) {
+        float2 sq = make_float2(0.f, 0.f), sk = sq;
+        for (int t = 0; t < tiles; ++t) {
+            const size_t e = ((size_t)t * rows + row) * KP2 + pi;
+            const float2 x = reinterpret_cast<const float2*>(dq_part)[e];
+            const float2 y = reinterpret_cast<const float2*>(dk_part)[e];
+            sq.x += x.x, sq.y += x.y, sk.x += y.x, sk.y += y.y;
+        }
+        const int kc = 2 * pi;
+        if (kc < p.K) {
+            st1(dq, row * p.K + kc, sq.x, p.io_dtype);
+            st1(dk, row * p.K + kc, sk.x, p.io_dtype);
+        }
+        if (kc + 1 < p.K) {
+            st1(dq, row * p.K + kc + 1, sq.y, p.io_dtype);
+            st1(dk, row * p.K + kc + 1, sk.y, p.io_dtype);
+        }
+    }
+    if (lane == 0) {
+        float df = 0.f, dip = 0.f;
+        for (int t = 0; t < tiles; ++t) {
+            df += df_part[(size_t)t * rows + row];
+            dip += dip_part[(size_t)t * rows + row];
+        }
+        const float gtv = p.gt[row], gh = p.g[h];
+        const float f = expf(-gtv * gh);
+        dgt[row] = -gh * f * df;
+        w_dg[row] = -gtv * f * df;
+        w_dip[row] = dip;
+    }
+}
+
+// ---- finishing kernel 2: one CTA per head, ordered sum over all rows -----------------------------------
+__global__ void __launch_bounds__(256) bwd_finish_heads(const float* __restrict__ w_dg, const float* __restrict__ w_dip,
+                                                       float* dg, float* dIp, long long tokens, int H) {
+    __shared__ float s0[256], s1[256];
+    const int h = blockIdx.x, tid = threadIdx.x;
+    float a0 = 0.f, a1 = 0.f;
+    for (long long t = tid; t < tokens; t += 256) {
+        a0 += w_dg[t * H + h];
+        a1 += w_dip[t * H + h];
+    }
+    s0[tid] = a0;
+    s1[tid] = a1;
+    __syncthreads();
+    for (int s = 128; s >= 1; s >>= 1) {
+        if (tid < s) {
+            s0[tid] += s0[tid + s];
+            s1[tid] += s1[tid + s];
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        dg[h] = s0[0];
+        dIp[h] = s1[0];
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
+// Host side
+// -------------------------------------------------------------------------------------------------
+struct BwdShape {
+    int RK, KG, RV;
+};
+static BwdShape bwd_shape(int KP) {
+    switch (KP) {
+        case 16: return {2, 8, 2};
+        case 32: return {4, 8, 2};
+        case 48: return {6, 8, 2};
+        case 64: return {4, 16, 2};
+        case 96: return {6, 16, 2};
+        case 128: return {4, 32, 2};
+        case 192: return {6, 32, 2};
+        case 256: return {8, 32, 1};
+        default: return {0, 0, 0};
+    }
+}
+// Warps per CTA: 8 (4 for short d_v or, to fit shared memory, for the widest d_k tiles).
+static int bwd_warps(int KP, int rpw, int V) {
+    if (rpw == 1) return 8;
+    if (KP >= 192) return 4;
+    return V > 4 * rpw ? 8 : 4;
+}
+
+int bwd_tile_rows(int K, int V) {
+    const BwdShape s = bwd_shape(palimpsa_padded_k(K));
+    if (!s.RK) return 0;
+    const int rpw = (32 / s.KG) * s.RV;
+    return bwd_warps(s.RK * s.KG, rpw, V) * rpw;
+}
+
+BwdWorkspace bwd_workspace_layout(const palimpsa_problem& p) {
+    BwdWorkspace ws{};
+    ws.KP = palimpsa_padded_k(p.K);
+    const int TV = bwd_tile_rows(p.K, p.V);
+    if (!TV) return ws;
+    ws.tiles = (p.V + TV - 1) / TV;
+    const size_t rows = (size_t)p.total_tokens * p.H;
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        size_t o = off;
+        off += (bytes + 255) / 256 * 256;
+        return o;
+    };
+    ws.dq_part = take((size_t)ws.tiles * rows * ws.KP * 4);
+    ws.dk_part = take((size_t)ws.tiles * rows * ws.KP * 4);
+    ws.df_part = take((size_t)ws.tiles * rows * 4);
+    ws.dip_part = take((size_t)ws.tiles * rows * 4);
+    ws.w_dg = take(rows * 4);
+    ws.w_dip = take(rows * 4);
+    ws.total = off;
+    return ws;
+}
+
+template <int RK, int KG, int RV>
+static int launch_bwd_t(const BwdArgs& a, int tiles, cudaStream_t stream) {
+    constexpr int VG = 32 / KG, RPW = VG * RV;
+    const palimpsa_problem& p = a.p;
+    const int W = bwd_warps(RK * KG, RPW, p.V);
+    const int TV = W * RPW;
+    const bool unc = (p.flags & PALIMPSA_FLAG_UNCERTAINTY) != 0;
+    const BwdSmem L = bwd_smem_layout(RK * KG, TV, RV * RK, 32 * W, W * VG, dtype_size(p.io_dtype), unc);
+    if (L.total > 227 * 1024) return PALIMPSA_E_DIM;
+    dim3 grid(tiles, p.num_seqs * p.H, 1);
+    dim3 block(32 * W, 1, 1);
+    cudaError_t e;
+    if (unc) {
+        e = cudaFuncSetAttribute(bwd_kernel<RK, KG, RV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+        if (e != cudaSuccess) return PALIMPSA_E_LAUNCH;
+        bwd_kernel<RK, KG, RV, true><<<grid, block, L.total, stream>>>(a);
+    } else {
+        e = cudaFuncSetAttribute(bwd_kernel<RK, KG, RV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+        if (e != cudaSuccess) return PALIMPSA_E_LAUNCH;
+        bwd_kernel<RK, KG, RV, false><<<grid, block, L.total, stream>>>(a);
+    }
+    return cudaGetLastError() == cudaSuccess ? PALIMPSA_OK : PALIMPSA_E_LAUNCH;
+}
+
+static bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
+
+int launch_bwd(const palimpsa_bwd_params* prm, cudaStream_t stream) {
+    const palimpsa_problem& p = prm->p;
+    const BwdWorkspace ws = bwd_workspace_layout(p);
+    if (!ws.tiles) return PALIMPSA_E_DIM;
+    char* base = reinterpret_cast<char*>(prm->workspace);
+    BwdArgs a;
+    a.p = p;
+    a.d_o = prm->d_o;
+    a.d_o_var = (p.flags & PALIMPSA_FLAG_UNCERTAINTY) ? prm->d_o_var : nullptr;
+    a.ckpt_M = prm->ckpt_M;
+    a.ckpt_I = prm->ckpt_I;
+    a.dq_part = reinterpret_cast<float*>(base + ws.dq_part);
+    a.dk_part = reinterpret_cast<float*>(base + ws.dk_part);
+    a.df_part = reinterpret_cast<float*>(base + ws.df_part);
+    a.dip_part = reinterpret_cast<float*>(base + ws.dip_part);
+    a.dv = prm->dv;
+    a.db = prm->db;
+    a.rows_total = p.total_tokens * p.H;
+    const int es = dtype_size(p.io_dtype);
+    a.aligned = ((p.K * es) % 16 == 0) && ((p.V * es) % 16 == 0) && aligned16(p.q) && aligned16(p.k) &&
+                aligned16(p.v) && aligned16(p.b) && aligned16(prm->d_o) &&
+                (a.d_o_var == nullptr || aligned16(a.d_o_var)) && ((reinterpret_cast<uintptr_t>(p.gt) & 3) == 0);
+    int rc;
+    switch (ws.KP) {
+        case 16: rc = launch_bwd_t<2, 8, 2>(a, ws.tiles, stream); break;
+        case 32: rc = launch_bwd_t<4, 8, 2>(a, ws.tiles, stream); break;
+        case 48: rc = launch_bwd_t<6, 8, 2>(a, ws.tiles, stream); break;
+        case 64: rc = launch_bwd_t<4, 16, 2>(a, ws.tiles, stream); break;
+        case 96: rc = launch_bwd_t<6, 16, 2>(a, ws.tiles, stream); break;
+        case 128: rc = launch_bwd_t<4, 32, 2>(a, ws.tiles, stream); break;
+        case 192: rc = launch_bwd_t<6, 32, 2>(a, ws.tiles, stream); break;
+        case 256: rc = launch_bwd_t<8, 32, 1>(a, ws.tiles, stream); break;
+        default: return PALIMPSA_E_DIM;
+    }
+    if (rc != PALIMPSA_OK) return rc;
+    const long long rows = a.rows_total;
+    if (rows > 0) {
+        const int wpb = 8;
+        bwd_finish_rows<<<(unsigned)((rows + wpb - 1) / wpb), 32 * wpb, 0, stream>>>(
+            p, a.dq_part, a.dk_part, a.df_part, a.dip_part, prm->dq, prm->dk, prm->dgt,
+            reinterpret_cast<float*>(base + ws.w_dg), reinterpret_cast<float*>(base + ws.w_dip), ws.tiles, ws.KP, rows);
+        if (cudaGetLastError() != cudaSuccess) return PALIMPSA_E_LAUNCH;
+    }
+    bwd_finish_heads<<<p.H, 256, 0, stream>>>(reinterpret_cast<float*>(base + ws.w_dg),
+                                              reinterpret_cast<float*>(base + ws.w_dip), prm->dg, prm->dIp,
+                                              p.total_tokens, p.H);
+    return cudaGetLastError() == cudaSuccess ? PALIMPSA_OK : PALIMPSA_E_LAUNCH;
+}
+
+}  // namespace palimpsa

@@ -1,0 +1,444 @@
+// Forward kernel of the Palimpsa operator (sm_100a).
+//
+// One CTA owns a tile of TV state rows (d_v) x all KP state columns (padded d_k) of one
+// (sequence, head) and walks that sequence's tokens in order with the (M, I) state pair held in
+// registers for the whole walk.  Work per state element and token: 6 packed-FP32 lane ops and one
+// MUFU reciprocal -- the kernel is bound by the MUFU pipe, not by HBM.
+//
+//   thread layout   lane = vg*KG + kg.  A thread owns RV=2 rows x RK columns; the KG lanes of a
+//                   row group own interleaved float4 column groups (column = 4*(j*KG+kg)+i), so
+//                   that shared-memory operand reads and global state accesses of a warp are
+//                   contiguous.
+//   staging         blocks of 16 tokens: cp.async (16 B) into a raw double buffer one block
+//                   ahead, then one cooperative pass converts to fp32 operands (q*scale, k, k*k,
+//                   v, b, f = exp(-gt*g), c = (1-f)*Ip) shared by every thread of the CTA.
+//   reduction       o[v] = sum_k: in-thread over RK, then log2(KG) xor-shuffles.
+//   checkpoints     optional (M, I) store at the start of every 16-token block (for backward).
+//
+// It serves the chunked op, the fused-recurrent op and the single-token decode step: what the
+// reference does with chunk_palimpsa_fwd_kernel (chunk_palimpsa_forgetting_scalar.py:66-218) and
+// fused_palimpsa_recurrent_fwd_kernel (fused_recurrent_palimpsa.py:24-154).
+#include "common.cuh"
+#include "host.h"
+
+namespace palimpsa {
+
+struct FwdArgs {
+    palimpsa_problem p;
+    void* o;
+    void* o_var;
+    float* final_mu;
+    float* final_I;
+    float* ckpt_M;
+    float* ckpt_I;
+    int aligned;  // 1: every io row is 16-byte aligned and a multiple of 16 bytes
+};
+
+struct FwdSmem {
+    int qs, ks, kks, qqs, vs, bs, fc, ys, yvs;  // fp32 operand / result buffers (byte offsets)
+    int raw;                                    // two raw stages follow each other from here
+    int rq, rk, rv, rb, rgt, raw_stage;         // offsets inside a stage, stage size
+    int total;
+};
+
+__host__ __device__ inline FwdSmem fwd_smem_layout(int KP, int TV, int es, bool unc) {
+    FwdSmem s;
+    int off = 0;
+    auto take = [&](int bytes) {
+        int o = off;
+        off += round_up(bytes, 16);
+        return o;
+    };
+    s.qs = take(TB * KP * 4);
+    s.ks = take(TB * KP * 4);
+    s.kks = take(TB * KP * 4);
+    s.qqs = unc ? take(TB * KP * 4) : 0;
+    s.vs = take(TB * TV * 4);
+    s.bs = take(TB * TV * 4);
+    s.fc = take(TB * 8);
+    s.ys = take(TB * TV * 4);
+    s.yvs = unc ? take(TB * TV * 4) : 0;
+    s.raw = off;
+    int r = 0;
+    auto rtake = [&](int bytes) {
+        int o = r;
+        r += round_up(bytes, 16);
+        return o;
+    };
+    s.rq = rtake(TB * KP * es);
+    s.rk = rtake(TB * KP * es);
+    s.rv = rtake(TB * TV * es);
+    s.rb = rtake(TB * TV * es);
+    s.rgt = rtake(TB * 4);
+    s.raw_stage = r;
+    s.total = off + 2 * r;
+    return s;
+}
+
+// Issue the asynchronous copies of one block of nt tokens (aligned fast path only).
+__device__ __forceinline__ void fwd_issue(const FwdArgs& a, unsigned char* stage, const FwdSmem& L, int es, int KP,
+                                          int TV, long long tok0, int nt, int h, int v0, int tvw) {
+    const palimpsa_problem& p = a.p;
+    const int nthr = blockDim.x, tid = threadIdx.x;
+    const int cq = p.K * es / 16;
+    const char* gq = reinterpret_cast<const char*>(p.q);
+    const char* gk = reinterpret_cast<const char*>(p.k);
+    for (int i = tid; i < nt * cq; i += nthr) {
+        int t = i / cq, c = i - t * cq;
+        long long src = ((tok0 + t) * p.H + h) * (long long)p.K * es + c * 16;
+        int dst = t * KP * es + c * 16;
+        cp_async16(stage + L.rq + dst, gq + src);
+        cp_async16(stage + L.rk + dst, gk + src);
+    }
+    const int cv = tvw * es / 16;
+    const char* gv = reinterpret_cast<const char*>(p.v);
+    const char* gb = reinterpret_cast<const char*>(p.b);
+    for (int i = tid; i < nt * cv; i += nthr) {
+        int t = i / cv, c = i - t * cv;
+        long long src = (((tok0 + t) * p.H + h) * (long long)p.V + v0) * es + c * 16;
+        int dst = t * TV * es + c * 16;
+        cp_async16(stage + L.rv + dst, gv + src);
+        cp_async16(stage + L.rb + dst, gb + src);
+    }
+    for (int i = tid; i < nt; i += nthr) cp_async4(stage + L.rgt + i * 4, p.gt + (tok0 + i) * p.H + h);
+}
+
+// Convert one block to fp32 operands.  ALIGNED: read the raw stage; otherwise read global memory
+// element by element (any K, V, alignment).
+template <int DT, bool ALIGNED, bool UNC>
+__device__ __forceinline__ void fwd_convert(const FwdArgs& a, unsigned char* sm, const unsigned char* stage,
+                                            const FwdSmem& L, int KP, int TV, long long tok0, int nt, int h, int v0,
+                                            float gh, float iph) {
+    const palimpsa_problem& p = a.p;
+    const int nthr = blockDim.x, tid = threadIdx.x;
+    const int K4 = KP / 4, V4 = TV / 4;
+    float4* qs = reinterpret_cast<float4*>(sm + L.qs);
+    float4* ks = reinterpret_cast<float4*>(sm + L.ks);
+    float4* kks = reinterpret_cast<float4*>(sm + L.kks);
+    float4* qqs = reinterpret_cast<float4*>(sm + L.qqs);
+    const float sc = p.scale;
+    for (int i = tid; i < TB * K4; i += nthr) {
+        int t = i / K4, c4 = i - t * K4;
+        float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), kv = qv;
+        if (t < nt && c4 * 4 < p.K) {
+            if (ALIGNED) {
+                qv = ld4<DT>(stage + L.rq, i);
+                kv = ld4<DT>(stage + L.rk, i);
+            } else {
+                long long row = ((tok0 + t) * p.H + h) * (long long)p.K;
+                qv = ld4_guarded<DT>(p.q, row + c4 * 4, row + p.K);
+                kv = ld4_guarded<DT>(p.k, row + c4 * 4, row + p.K);
+            }
+        }
+        qs[i] = make_float4(qv.x * sc, qv.y * sc, qv.z * sc, qv.w * sc);
+        ks[i] = kv;
+        kks[i] = make_float4(kv.x * kv.x, kv.y * kv.y, kv.z * kv.z, kv.w * kv.w);
+        if (UNC) qqs[i] = make_float4(sc * qv.x * qv.x, sc * qv.y * qv.y, sc * qv.z * qv.z, sc * qv.w * qv.w);
+    }
+    float4* vs = reinterpret_cast<float4*>(sm + L.vs);
+    float4* bs = reinterpret_cast<float4*>(sm + L.bs);
+    for (int i = tid; i < TB * V4; i += nthr) {
+        int t = i / V4, c4 = i - t * V4;
+        float4 vv = make_float4(0.f, 0.f, 0.f, 0.f), bv = vv;
+        if (t < nt && v0 + c4 * 4 < p.V) {
+            if (ALIGNED) {
+                vv = ld4<DT>(stage + L.rv, i);
+                bv = ld4<DT>(stage + L.rb, i);
+            } else {
+                long long row = ((tok0 + t) * p.H + h) * (long long)p.V;
+                vv = ld4_guarded<DT>(p.v, row + v0 + c4 * 4, row + p.V);
+                bv = ld4_guarded<DT>(p.b, row + v0 + c4 * 4, row + p.V);
+            }
+        }
+        vs[i] = vv;
+        bs[i] = bv;
+    }
+    float2* fc = reinterpret_cast<float2*>(sm + L.fc);
+    for (int i = tid; i < TB; i += nthr) {
+        float gtv = 0.f;
+        if (i < nt) gtv = ALIGNED ? reinterpret_cast<const float*>(stage + L.rgt)[i] : p.gt[(tok0 + i) * p.H + h];
+        float f = expf(-gtv * gh);
+        fc[i] = make_float2(f, (1.f - f) * iph);
+    }
+}
+
+template <int RK, int KG, bool UNC>
+__global__ void __launch_bounds__(128) fwd_kernel(const FwdArgs a) {
+    constexpr int KP = RK * KG, VG = 32 / KG, RV = 2, J4 = RK / 4;
+    extern __shared__ __align__(16) unsigned char sm[];
+    const palimpsa_problem& p = a.p;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, W = blockDim.x >> 5;
+    const int TV = W * VG * RV;
+    const int kg = lane % KG, vg = lane / KG;
+    const int row0 = (w * VG + vg) * RV;
+    const int n = blockIdx.y / p.H, h = blockIdx.y - n * p.H;
+    const int v0 = blockIdx.x * TV;
+    const int tvw = min(TV, p.V - v0);
+    const int es = dtype_size(p.io_dtype);
+    const FwdSmem L = fwd_smem_layout(KP, TV, es, UNC);
+    int bos, len;
+    seq_range(p, n, bos, len);
+    const float gh = p.g[h], iph = p.Ip[h];
+    const int K = p.K, V = p.V;
+    const bool vecK = (K % 4) == 0;
+
+    // ---- state registers ------------------------------------------------------------------
+    float2 M[RV][J4][2], I[RV][J4][2];
+    const long long st_base = ((long long)n * p.H + h) * V;
+#pragma unroll
+    for (int r = 0; r < RV; ++r) {
+        const int vrow = v0 + row0 + r;
+#pragma unroll
+        for (int j = 0; j < J4; ++j) {
+            const int kc = 4 * (j * KG + kg);
+            float4 m4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            float4 i4 = make_float4(1.f, 1.f, 1.f, 1.f);
+            if (vrow < V && kc < K) {
+                if (p.init_mu) {
+                    const long long e = (st_base + vrow) * K + kc;
+                    float4 mu4;
+                    if (vecK) {
+                        mu4 = *reinterpret_cast<const float4*>(p.init_mu + e);
+                        i4 = *reinterpret_cast<const float4*>(p.init_I + e);
+                    } else {
+                        const long long lim = (st_base + vrow + 1) * K;
+                        mu4 = ld4_guarded<PALIMPSA_F32>(p.init_mu, e, lim);
+                        i4 = ld4_guarded<PALIMPSA_F32>(p.init_I, e, lim);
+                        if (kc + 1 >= K) i4.y = 1.f;
+                        if (kc + 2 >= K) i4.z = 1.f;
+                        if (kc + 3 >= K) i4.w = 1.f;
+                    }
+                    m4 = make_float4(mu4.x * i4.x, mu4.y * i4.y, mu4.z * i4.z, mu4.w * i4.w);
+                } else {
+                    i4 = make_float4(iph, iph, iph, iph);
+                }
+            }
+            M[r][j][0] = make_float2(m4.x, m4.y);
+            M[r][j][1] = make_float2(m4.z, m4.w);
+            I[r][j][0] = make_float2(i4.x, i4.y);
+            I[r][j][1] = make_float2(i4.z, i4.w);
+        }
+    }
+
+    const int nblk = (len + TB - 1) / TB;
+    const long long slot0 = seq_first_slot(p, n);
+    const float4* qs4 = reinterpret_cast<const float4*>(sm + L.qs);
+    const float4* ks4 = reinterpret_cast<const float4*>(sm + L.ks);
+    const float4* kks4 = reinterpret_cast<const float4*>(sm + L.kks);
+    const float4* qqs4 = reinterpret_cast<const float4*>(sm + L.qqs);
+    const float* vs = reinterpret_cast<const float*>(sm + L.vs);
+    const float* bs = reinterpret_cast<const float*>(sm + L.bs);
+    const float2* fc = reinterpret_cast<const float2*>(sm + L.fc);
+    float* ys = reinterpret_cast<float*>(sm + L.ys);
+    float* yvs = reinterpret_cast<float*>(sm + L.yvs);
+    unsigned char* raw = sm + L.raw;
+
+    if (a.aligned && nblk > 0) {
+        fwd_issue(a, raw, L, es, KP, TV, bos, min(TB, len), h, v0, tvw);
+        cp_async_commit();
+    }
+
+    for (int blk = 0; blk < nblk; ++blk) {
+        const int t0 = blk * TB;
+        const int nt = min(TB, len - t0);
+        const long long tok0 = (long long)bos + t0;
+        unsigned char* stage = raw + (blk & 1) * L.raw_stage;
+        if (a.aligned) {
+            if (blk + 1 < nblk) {
+                fwd_issue(a, raw + ((blk + 1) & 1) * L.raw_stage, L, es, KP, TV, tok0 + TB, min(TB, len - t0 - TB), h,
+                          v0, tvw);
+                cp_async_commit();
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+        }
+        __syncthreads();
+        if (a.aligned) {
+            if (p.io_dtype == PALIMPSA_BF16)
+                fwd_convert<PALIMPSA_BF16, true, UNC>(a, sm, stage, L, KP, TV, tok0, nt, h, v0, gh, iph);
+            else if (p.io_dtype == PALIMPSA_F32)
+                fwd_convert<PALIMPSA_F32, true, UNC>(a, sm, stage, L, KP, TV, tok0, nt, h, v0, gh, iph);
+            else
+                fwd_convert<PALIMPSA_F16, true, UNC>(a, sm, stage, L, KP, TV, tok0, nt, h, v0, gh, iph);
+        } else {
+            if (p.io_dtype == PALIMPSA_BF16)
+                fwd_convert<PALIMPSA_BF16, false, UNC>(a, sm, stage, L, KP, TV, tok0, nt, h, v0, gh, iph);
+            else if (p.io_dtype == PALIMPSA_F32)
+                fwd_convert<PALIMPSA_F32, false, UNC>(a, sm, stage, L, KP, TV, tok0, nt, h, v0, gh, iph);
+            else
+                fwd_convert<PALIMPSA_F16, false, UNC>(a, sm, stage, L, KP, TV, tok0, nt, h, v0, gh, iph);
+        }
+        __syncthreads();
+
+        // ---- checkpoint: state before the first token of this block ---------------------------
+        if (a.ckpt_M) {
+            const long long cbase = ((slot0 + blk) * p.H + h) * V;
+#pragma unroll
+            for (int r = 0; r < RV; ++r) {
+                const int vrow = v0 + row0 + r;
+                if (vrow < V) {
+#pragma unroll
+                    for (int j = 0; j < J4; ++j) {
+                        const long long e = (cbase + vrow) * KP + 4 * (j * KG + kg);
+                        *reinterpret_cast<float4*>(a.ckpt_M + e) =
+                            make_float4(M[r][j][0].x, M[r][j][0].y, M[r][j][1].x, M[r][j][1].y);
+                        *reinterpret_cast<float4*>(a.ckpt_I + e) =
+                            make_float4(I[r][j][0].x, I[r][j][0].y, I[r][j][1].x, I[r][j][1].y);
+                    }
+                }
+            }
+        }
+
+        // ---- the recurrence --------------------------------------------------------------------
+        for (int t = 0; t < nt; ++t) {
+            const float2 fcv = fc[t];
+            const float2 ff = dup2(fcv.x), cc = dup2(fcv.y);
+            const float2 vv = *reinterpret_cast<const float2*>(vs + t * TV + row0);
+            const float2 bv = *reinterpret_cast<const float2*>(bs + t * TV + row0);
+            const float2 vr[RV] = {dup2(vv.x), dup2(vv.y)};
+            const float2 br[RV] = {dup2(bv.x), dup2(bv.y)};
+            float2 acc[RV], accv[RV];
+#pragma unroll
+            for (int r = 0; r < RV; ++r) acc[r] = accv[r] = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < J4; ++j) {
+                const int idx = t * (KP / 4) + j * KG + kg;
+                const float4 k4 = ks4[idx], kk4 = kks4[idx], q4 = qs4[idx];
+                float4 qq4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (UNC) qq4 = qqs4[idx];
+                const float2 kp[2] = {make_float2(k4.x, k4.y), make_float2(k4.z, k4.w)};
+                const float2 kkp[2] = {make_float2(kk4.x, kk4.y), make_float2(kk4.z, kk4.w)};
+                const float2 qp[2] = {make_float2(q4.x, q4.y), make_float2(q4.z, q4.w)};
+                const float2 qqp[2] = {make_float2(qq4.x, qq4.y), make_float2(qq4.z, qq4.w)};
+#pragma unroll
+                for (int r = 0; r < RV; ++r) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        M[r][j][e] = ffma2(ff, M[r][j][e], fmul2(vr[r], kp[e]));
+                        I[r][j][e] = ffma2(ff, I[r][j][e], ffma2(br[r], kkp[e], cc));
+                        const float2 rr = rcp2(I[r][j][e]);
+                        acc[r] = ffma2(fmul2(M[r][j][e], rr), qp[e], acc[r]);
+                        if (UNC) accv[r] = ffma2(rr, qqp[e], accv[r]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < RV; ++r) {
+                float y = acc[r].x + acc[r].y;
+                float yv = accv[r].x + accv[r].y;
+#pragma unroll
+                for (int off = KG / 2; off >= 1; off >>= 1) {
+                    y += __shfl_xor_sync(0xffffffffu, y, off);
+                    if (UNC) yv += __shfl_xor_sync(0xffffffffu, yv, off);
+                }
+                if (kg == 0) {
+                    ys[t * TV + row0 + r] = y;
+                    if (UNC) yvs[t * TV + row0 + r] = yv;
+                }
+            }
+        }
+        __syncthreads();
+
+        // ---- write the block's outputs -----------------------------------------------------------
+        for (int i = tid; i < nt * TV; i += blockDim.x) {
+            const int t = i / TV, r = i - t * TV;
+            if (r < tvw) {
+                const long long e = ((tok0 + t) * p.H + h) * (long long)V + v0 + r;
+                st1(a.o, e, ys[i], p.io_dtype);
+                if (UNC) st1(a.o_var, e, yvs[i], p.io_dtype);
+            }
+        }
+    }
+
+    // ---- final state in the API's (mu, I) form ---------------------------------------------------
+    if (a.final_mu) {
+#pragma unroll
+        for (int r = 0; r < RV; ++r) {
+            const int vrow = v0 + row0 + r;
+#pragma unroll
+            for (int j = 0; j < J4; ++j) {
+                const int kc = 4 * (j * KG + kg);
+                if (vrow < V && kc < K) {
+                    const float4 i4 = make_float4(I[r][j][0].x, I[r][j][0].y, I[r][j][1].x, I[r][j][1].y);
+                    const float4 mu4 = make_float4(M[r][j][0].x / i4.x, M[r][j][0].y / i4.y, M[r][j][1].x / i4.z,
+                                                   M[r][j][1].y / i4.w);
+                    const long long e = (st_base + vrow) * K + kc;
+                    if (vecK) {
+                        *reinterpret_cast<float4*>(a.final_mu + e) = mu4;
+                        *reinterpret_cast<float4*>(a.final_I + e) = i4;
+                    } else {
+                        const float mus[4] = {mu4.x, mu4.y, mu4.z, mu4.w};
+                        const float is[4] = {i4.x, i4.y, i4.z, i4.w};
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            if (kc + c < K) {
+                                a.final_mu[e + c] = mus[c];
+                                a.final_I[e + c] = is[c];
+                            }
+                    }
+                }
+            }
+        }
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
+// Host side
+// -------------------------------------------------------------------------------------------------
+template <int RK, int KG>
+static int launch_fwd_t(const FwdArgs& a, cudaStream_t stream) {
+    constexpr int VG = 32 / KG, RPW = VG * 2;  // state rows per warp
+    const palimpsa_problem& p = a.p;
+    int W = 4;
+    if (p.V <= RPW && RPW >= 8)
+        W = 1;
+    else if (p.V <= 2 * RPW)
+        W = 2;
+    const int TV = W * RPW;
+    const bool unc = (p.flags & PALIMPSA_FLAG_UNCERTAINTY) != 0;
+    const FwdSmem L = fwd_smem_layout(RK * KG, TV, dtype_size(p.io_dtype), unc);
+    dim3 grid((p.V + TV - 1) / TV, p.num_seqs * p.H, 1);
+    dim3 block(32 * W, 1, 1);
+    cudaError_t e;
+    if (unc) {
+        e = cudaFuncSetAttribute(fwd_kernel<RK, KG, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+        if (e != cudaSuccess) return PALIMPSA_E_LAUNCH;
+        fwd_kernel<RK, KG, true><<<grid, block, L.total, stream>>>(a);
+    } else {
+        e = cudaFuncSetAttribute(fwd_kernel<RK, KG, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+        if (e != cudaSuccess) return PALIMPSA_E_LAUNCH;
+        fwd_kernel<RK, KG, false><<<grid, block, L.total, stream>>>(a);
+    }
+    return cudaGetLastError() == cudaSuccess ? PALIMPSA_OK : PALIMPSA_E_LAUNCH;
+}
+
+static bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
+
+int launch_fwd(const palimpsa_fwd_params* prm, cudaStream_t stream) {
+    FwdArgs a;
+    a.p = prm->p;
+    a.o = prm->o;
+    a.o_var = prm->o_var;
+    a.final_mu = prm->final_mu;
+    a.final_I = prm->final_I;
+    a.ckpt_M = prm->ckpt_M;
+    a.ckpt_I = prm->ckpt_I;
+    const palimpsa_problem& p = a.p;
+    const int es = dtype_size(p.io_dtype);
+    a.aligned = ((p.K * es) % 16 == 0) && ((p.V * es) % 16 == 0) && aligned16(p.q) && aligned16(p.k) &&
+                aligned16(p.v) && aligned16(p.b) && ((reinterpret_cast<uintptr_t>(p.gt) & 3) == 0);
+    switch (palimpsa_padded_k(p.K)) {
+        case 16: return launch_fwd_t<8, 2>(a, stream);
+        case 32: return launch_fwd_t<8, 4>(a, stream);
+        case 48: return launch_fwd_t<12, 4>(a, stream);
+        case 64: return launch_fwd_t<16, 4>(a, stream);
+        case 96: return launch_fwd_t<12, 8>(a, stream);
+        case 128: return launch_fwd_t<16, 8>(a, stream);
+        case 192: return launch_fwd_t<12, 16>(a, stream);
+        case 256: return launch_fwd_t<16, 16>(a, stream);
+        default: return PALIMPSA_E_DIM;
+    }
+}
+
+}  // namespace palimpsa

@@ -1,0 +1,29 @@
+// Host-side declarations shared by the translation units of libpalimpsa_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "../../include/palimpsa_b200.h"
+
+namespace palimpsa {
+
+// Enqueue the forward kernel (fwd.cu).  Parameters are assumed validated.
+int launch_fwd(const palimpsa_fwd_params* prm, cudaStream_t stream);
+
+// Backward (bwd.cu): main kernel + the two finishing kernels.
+int launch_bwd(const palimpsa_bwd_params* prm, cudaStream_t stream);
+
+// State rows (d_v) one backward CTA owns for this problem; the number of row tiles follows.
+int bwd_tile_rows(int K, int V);
+
+// Layout of the backward scratch memory (byte offsets from a 256-byte aligned base).
+struct BwdWorkspace {
+    size_t dq_part, dk_part;    // float [tiles][tokens*H][KP]
+    size_t df_part, dip_part;   // float [tiles][tokens*H]
+    size_t w_dg, w_dip;         // float [tokens*H]
+    size_t total;
+    int tiles, KP;
+};
+BwdWorkspace bwd_workspace_layout(const palimpsa_problem& p);
+
+}  // namespace palimpsa

@@ -1,0 +1,5 @@
+from .chunk import chunk_palimpsa
+from .fused_recurrent import fused_recurrent_palimpsa
+from .naive import palimpsa_ref
+
+__all__ = ["palimpsa_ref", "chunk_palimpsa", "fused_recurrent_palimpsa"]
