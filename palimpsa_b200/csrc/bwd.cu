@@ -616,24 +616,38 @@ static BwdShape bwd_shape(int KP) {
         default: return {0, 0, 0};
     }
 }
-// Warps per CTA: 8 (4 for short d_v or, to fit shared memory, for the widest d_k tiles).
-static int bwd_warps(int KP, int rpw, int V) {
-    if (rpw == 1) return 8;
-    if (KP >= 192) return 4;
-    return V > 4 * rpw ? 8 : 4;
+// Warps per CTA: 8 when d_v is long enough to use them and the shared-memory layout fits, else 4.
+struct BwdConfig {
+    BwdShape s;
+    int W, TV, smem;
+};
+static BwdConfig bwd_config(const palimpsa_problem& p) {
+    BwdConfig c{};
+    c.s = bwd_shape(palimpsa_padded_k(p.K));
+    if (!c.s.RK) return c;
+    const int VG = 32 / c.s.KG, rpw = VG * c.s.RV, KP = c.s.RK * c.s.KG;
+    const bool unc = (p.flags & PALIMPSA_FLAG_UNCERTAINTY) != 0;
+    const int es = dtype_size(p.io_dtype);
+    int W = (rpw == 1 || p.V > 4 * rpw) ? 8 : 4;
+    for (;;) {
+        c.W = W;
+        c.TV = W * rpw;
+        c.smem = bwd_smem_layout(KP, c.TV, c.s.RV * c.s.RK, 32 * W, W * VG, es, unc).total;
+        if (c.smem <= 227 * 1024 || W == 4 || rpw == 1) break;
+        W = 4;
+    }
+    return c;
 }
 
-int bwd_tile_rows(int K, int V) {
-    const BwdShape s = bwd_shape(palimpsa_padded_k(K));
-    if (!s.RK) return 0;
-    const int rpw = (32 / s.KG) * s.RV;
-    return bwd_warps(s.RK * s.KG, rpw, V) * rpw;
+int bwd_tile_rows(const palimpsa_problem& p) {
+    const BwdConfig c = bwd_config(p);
+    return (c.s.RK && c.smem <= 227 * 1024) ? c.TV : 0;
 }
 
 BwdWorkspace bwd_workspace_layout(const palimpsa_problem& p) {
     BwdWorkspace ws{};
     ws.KP = palimpsa_padded_k(p.K);
-    const int TV = bwd_tile_rows(p.K, p.V);
+    const int TV = bwd_tile_rows(p);
     if (!TV) return ws;
     ws.tiles = (p.V + TV - 1) / TV;
     const size_t rows = (size_t)p.total_tokens * p.H;
@@ -655,10 +669,10 @@ BwdWorkspace bwd_workspace_layout(const palimpsa_problem& p) {
 
 template <int RK, int KG, int RV>
 static int launch_bwd_t(const BwdArgs& a, int tiles, cudaStream_t stream) {
-    constexpr int VG = 32 / KG, RPW = VG * RV;
+    constexpr int VG = 32 / KG;
     const palimpsa_problem& p = a.p;
-    const int W = bwd_warps(RK * KG, RPW, p.V);
-    const int TV = W * RPW;
+    const BwdConfig cfg = bwd_config(p);
+    const int W = cfg.W, TV = cfg.TV;
     const bool unc = (p.flags & PALIMPSA_FLAG_UNCERTAINTY) != 0;
     const BwdSmem L = bwd_smem_layout(RK * KG, TV, RV * RK, 32 * W, W * VG, dtype_size(p.io_dtype), unc);
     if (L.total > 227 * 1024) return PALIMPSA_E_DIM;

@@ -14,7 +14,7 @@ int launch_fwd(const palimpsa_fwd_params* prm, cudaStream_t stream);
 int launch_bwd(const palimpsa_bwd_params* prm, cudaStream_t stream);
 
 // State rows (d_v) one backward CTA owns for this problem; the number of row tiles follows.
-int bwd_tile_rows(int K, int V);
+int bwd_tile_rows(const palimpsa_problem& p);
 
 // Layout of the backward scratch memory (byte offsets from a 256-byte aligned base).
 struct BwdWorkspace {
