@@ -1,0 +1,375 @@
+#!/usr/bin/env python
+"""Benchmark of the Palimpsa operator hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c4]
+
+Workload (default ``c2``): the 170M-model-shaped layer op, chunked forward + backward in bf16 with
+fp32 state, B=8, T=4096, H=6, d_k=d_v=128, seeded synthetic inputs (q,k L2-normalised N(0,1);
+v ~ N(0,1); b = sigmoid(N); gt, g = softplus(N); Ip = 1; dO ~ N(0,1)).  One step = one forward and
+one backward over that batch.  With N > 1 GPUs every rank runs the same per-GPU batch on its own
+shard of a global batch of 8*N sequences: the op is independent per (sequence, head), so there is
+no data-path collective ("weak" scaling); ranks only meet at the timing barriers.
+
+Prints ONE JSON line (rank 0).  ``value`` is timed with inputs resident in HBM; ``e2e`` is the same
+step through the public Python API from pinned HOST buffers, host->device and device->host copies
+inside the timed region.  ``roofline`` describes the dominant kernel (the backward main kernel),
+timed alone with CUDA events through the staged C-ABI entry point.  ``cpu_baseline`` is the naive
+per-timestep recurrence (float32 port of the reference's ``palimpsa_ref``, forward + autograd
+backward) on this box's host cores, on a truncated sample.
+
+``--impl reference`` times only that CPU recurrence (the reference has no other CPU path).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+METRIC = "fwd+bwd tokens/s (chunk, bf16, T=4096)"
+C2 = dict(B=8, T=4096, H=6, K=128, V=128)
+C4 = dict(B=256, H=12, K=128, V=128)
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "source": "fallback"}
+
+
+def make_inputs(B, T, H, K, V, dtype, device, seed=0, pin=False):
+    """Seeded synthetic inputs drawn on the CPU generator in a fixed order (see module docstring)."""
+    gen = torch.Generator().manual_seed(seed)
+    rn = lambda *s: torch.randn(*s, generator=gen, dtype=torch.float32)
+    q = torch.nn.functional.normalize(rn(B, T, H, K), dim=-1)
+    k = torch.nn.functional.normalize(rn(B, T, H, K), dim=-1)
+    v = rn(B, T, H, V)
+    b = torch.sigmoid(rn(B, T, H, V))
+    gt = torch.nn.functional.softplus(rn(B, T, H))
+    g = torch.nn.functional.softplus(rn(H))
+    Ip = torch.ones(H)
+    do = rn(B, T, H, V)
+    host = {"q": q.to(dtype), "k": k.to(dtype), "v": v.to(dtype), "b": b.to(dtype), "gt": gt, "g": g, "Ip": Ip,
+            "do": do.to(dtype)}
+    if pin:
+        host = {n: x.pin_memory() for n, x in host.items()}
+    if device is None:
+        return host, None
+    return host, {n: x.to(device) for n, x in host.items()}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, val in zip(names, r[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline: the naive recurrence (port of the reference's palimpsa_ref), forward + autograd backward
+# ------------------------------------------------------------------------------------------------
+def cpu_step(inp):
+    from oracle.palimpsa_oracle import naive_recurrence_fp32
+    leaves = [inp[n].clone().requires_grad_(True) for n in ("q", "k", "v", "b", "gt", "g", "Ip")]
+    o = naive_recurrence_fp32(*leaves)
+    o.backward(inp["do"].to(o.dtype))
+    return o
+
+
+def cpu_baseline(budget_s, cfg, steps=1, warmup=0):
+    """Times the naive recurrence on a truncated sample (same B, H, d_k, d_v; T cut so that the whole
+    call stays within ``budget_s`` seconds).  Returns (tokens/s, description, per-step seconds)."""
+    B, H, K, V = cfg["B"], cfg["H"], cfg["K"], cfg["V"]
+    probe, _ = make_inputs(B, 4, H, K, V, torch.bfloat16, None, seed=1)
+    cpu_step(probe)                                   # first call pays one-time costs
+    t0 = time.perf_counter()
+    cpu_step(probe)
+    per_tok = (time.perf_counter() - t0) / 4
+    T = int(max(4, min(256, budget_s / max(per_tok, 1e-6) / max(1, steps + warmup))))
+    inp, _ = make_inputs(B, T, H, K, V, torch.bfloat16, None, seed=0)
+    for _ in range(warmup):
+        cpu_step(inp)
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        cpu_step(inp)
+        times.append(time.perf_counter() - t0)
+    best = min(times)
+    return B * T / best, f"B={B} H={H} d_k={K} d_v={V} bf16 inputs, T truncated to {T} (autograd through the " \
+                         f"naive loop keeps every step's state); best of {steps}", times
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    cores = torch.get_num_threads()
+    val, sample, times = cpu_baseline(150.0, C2, steps=args.steps, warmup=args.warmup)
+    ms = 1e3 * sum(times) / len(times)
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "C2 170M-shaped chunk fwd+bwd B=8 T=4096 H=6 d_k=d_v=128 (CPU sample truncated in T)"},
+            "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0, "host_cpus": os.cpu_count()}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+def fwd_bwd(d):
+    from palimpsa_b200.ops import chunk_palimpsa
+    leaves = [d[n].detach().requires_grad_(True) for n in ("q", "k", "v", "b", "gt", "g", "Ip")]
+    o = chunk_palimpsa(*leaves, chunk_size=64)
+    o.backward(d["do"])
+    return o, [x.grad for x in leaves]
+
+
+def time_region(fn, steps, warmup, world, dev):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def kernel_roofline(d, cfg, steps, peaks):
+    """Times the backward main kernel alone (CUDA events on its stream) through the C ABI."""
+    from palimpsa_b200 import _lib as L
+    from palimpsa_b200.ops.palimpsa import _core
+    lib = L.lib()
+    B, T, H, K, V = cfg["B"], cfg["T"], cfg["H"], cfg["K"], cfg["V"]
+    q, k, v, b, gt, g, Ip, do = [d[n] for n in ("q", "k", "v", "b", "gt", "g", "Ip", "do")]
+    with torch.no_grad():
+        _, _, _, _, ckM, ckI, _ = _core.fwd_op(q, k, v, b, gt, g, Ip, None, None, None, K ** -0.5, False, True, False,
+                                               False)
+    dq, dk, dv, db = [torch.empty_like(x) for x in (q, k, v, b)]
+    dgt = torch.empty(B, T, H, device=q.device)
+    dg, dIp = torch.empty(H, device=q.device), torch.empty(H, device=q.device)
+    prm = L.BwdParams()
+    prm.struct_size = C.sizeof(L.BwdParams)
+    prm.p = _core._problem(q, k, v, b, gt, g, Ip, None, None, None, None, K ** -0.5, 0)
+    need = lib.palimpsa_bwd_workspace_bytes(C.byref(prm.p))
+    ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+    prm.d_o, prm.ckpt_M, prm.ckpt_I = do.data_ptr(), ckM.data_ptr(), ckI.data_ptr()
+    prm.dq, prm.dk, prm.dv, prm.db = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), db.data_ptr()
+    prm.dgt, prm.dg, prm.dIp = dgt.data_ptr(), dg.data_ptr(), dIp.data_ptr()
+    prm.workspace, prm.workspace_bytes = ws.data_ptr(), ws.numel()
+    stream = torch.cuda.current_stream()
+    sp = C.c_void_p(stream.cuda_stream)
+    for _ in range(3):
+        L.check(lib.palimpsa_chunk_bwd_stages(C.byref(prm), sp, 1), "bwd main")
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(max(3, steps)):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        L.check(lib.palimpsa_chunk_bwd_stages(C.byref(prm), sp, 1), "bwd main")
+        e1.record(stream)
+        L.check(lib.palimpsa_chunk_bwd_stages(C.byref(prm), sp, 2), "bwd finish")
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    ms = sum(times) / len(times)
+    th = B * T * H                                   # token-heads per launch
+    es = q.element_size()
+    alg_bytes = th * ((2 * K + 3 * V) * es + 4 + (2 * K + 2 * V) * es + 4)   # q,k,v,b,do,gt in; dq,dk,dv,db,dgt out
+    flops = 30.0 * K * V * th                        # algorithmic lane-ops of the backward, per the operator's definition
+    achieved = alg_bytes / (ms * 1e-3) / 1e9
+    return {"bound": "hbm", "kernel": "bwd_kernel (backward main)", "achieved": achieved, "peak": peaks["hbm_gbs"],
+            "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"], "traffic": None,
+            "launch_ms": ms, "algorithmic_bytes_per_launch": alg_bytes,
+            "note": "the kernel is FP32-pipe bound, not HBM bound: see 'compute'",
+            "compute": {"algorithmic_tflops": flops / (ms * 1e-3) / 1e12, "flop_per_token_head": 30 * K * V}}
+
+
+def fp32_peaks(dev):
+    """Measured FP32 FMA and MUFU-reciprocal ceilings of this GPU (register-resident micro-benchmarks)."""
+    path = os.path.join(ROOT, "palimpsa_b200", "libpalimpsa_microbench.so")
+    if not os.path.exists(path):
+        return None
+    mb = C.CDLL(path)
+    sink = torch.zeros(16, device=dev)
+    out = {}
+    for kind, name in ((1, "fma_tflops"), (2, "rcp_tops"), (3, "fwd_mix_telem")):
+        ms, ops = C.c_float(), C.c_double()
+        rc = mb.palimpsa_microbench(kind, 148 * 8, 2048, 3, C.c_void_p(sink.data_ptr()), C.byref(ms), C.byref(ops))
+        if rc != 0:
+            return None
+        rate = ops.value / (ms.value * 1e-3) / 1e12
+        out[name] = rate * (2.0 if kind == 1 else 1.0)
+    return out
+
+
+def run_ours(args, rank, world, local_rank):
+    from palimpsa_b200 import _lib
+    _lib.lib()  # fail loudly if the CUDA library is missing
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    cfg = C2
+    B, T, H, K, V = cfg["B"], cfg["T"], cfg["H"], cfg["K"], cfg["V"]
+    host, d = make_inputs(B, T, H, K, V, torch.bfloat16, dev, seed=rank, pin=True)
+    tokens = B * T
+    in_bytes = sum(d[n].numel() * d[n].element_size() for n in ("q", "k", "v", "b", "do", "gt"))
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms = time_region(lambda: fwd_bwd(d), args.steps, args.warmup, world, dev)
+    clocks = sampler.stop() if sampler else None
+    value = world * tokens * args.steps / (ms * 1e-3)
+
+    # end to end: pinned host -> device, fwd+bwd, every result back to pinned host
+    names_in = ("q", "k", "v", "b", "gt", "g", "Ip", "do")
+    out_host = {}
+
+    def e2e_step():
+        dd = {n: host[n].to(dev, non_blocking=True) for n in names_in}
+        o, grads = fwd_bwd(dd)
+        for n, x in zip(("o", "dq", "dk", "dv", "db", "dgt", "dg", "dIp"), [o] + grads):
+            if n not in out_host:
+                out_host[n] = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
+            out_host[n].copy_(x, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_steps = max(3, min(args.steps, 10))
+    ms_e2e = time_region(e2e_step, e2e_steps, 3, world, dev)
+    e2e_val = world * tokens * e2e_steps / (ms_e2e * 1e-3)
+    h2d = sum(host[n].numel() * host[n].element_size() for n in names_in)
+    d2h = sum(x.numel() * x.element_size() for x in out_host.values())
+
+    if rank != 0:
+        return
+    peaks = measured_peaks()
+    roof = kernel_roofline(d, cfg, args.steps, peaks)
+    fp = fp32_peaks(dev)
+    if fp:
+        roof["compute"].update({"fp32_fma_peak_tflops_measured": fp["fma_tflops"],
+                                "mufu_rcp_peak_tops_measured": fp["rcp_tops"],
+                                "frac_of_fp32_peak": roof["compute"]["algorithmic_tflops"] / fp["fma_tflops"]})
+    del d
+    torch.cuda.empty_cache()
+    cb_val, cb_sample, _ = cpu_baseline(20.0, cfg, steps=2, warmup=0)
+    line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"C2 170M-shaped layer op: chunk fwd+bwd, bf16 io / fp32 state, B={B}/GPU T={T} "
+                                   f"H={H} d_k={K} d_v={V}", "io_dtype": "bf16", "global_batch": B * world,
+                       "sharding": "batch x head across GPUs, no collective",
+                       "l2": f"inputs per step {in_bytes / 2 ** 20:.0f} MiB > L2 {L2_BYTES // 2 ** 20} MiB (no flush needed)"},
+            "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": ms_e2e / e2e_steps},
+            "gpu_launches": 4 * args.steps, "clocks": clocks, "roofline": roof,
+            "cpu_baseline": {"value": cb_val, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": cb_sample}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile-case", action="store_true",
+                    help="run a few forward+backward steps of a half-size batch (B=4) and exit: the small case "
+                         "that profiler captures are taken on")
+    args = ap.parse_args()
+    if args.profile_case:
+        dev = torch.device("cuda", 0)
+        _, d = make_inputs(4, C2["T"], C2["H"], C2["K"], C2["V"], torch.bfloat16, dev)
+        for _ in range(3):
+            fwd_bwd(d)
+        torch.cuda.synchronize()
+        print("profile case done")
+        return
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

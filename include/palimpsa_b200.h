@@ -143,6 +143,12 @@ size_t palimpsa_bwd_workspace_bytes(const palimpsa_problem *p);
 /* Backward of the chunked op (ChunkPalimpsa.backward, chunk_palimpsa_forgetting_scalar.py:522-620). */
 int palimpsa_chunk_bwd(const palimpsa_bwd_params *params, void *cuda_stream);
 
+/* The same backward split in two: stages bit 0 = main kernel (fills the workspace partials, dv, db),
+ * bit 1 = finishing kernels (dq, dk, dgt, dg, dIp from the workspace).  Lets a caller time or
+ * overlap the two; stages == 3 equals palimpsa_chunk_bwd.  No counterpart in the reference, whose
+ * backward is one kernel plus torch reductions (chunk_palimpsa_forgetting_scalar.py:592-613). */
+int palimpsa_chunk_bwd_stages(const palimpsa_bwd_params *params, void *cuda_stream, int stages);
+
 /* Backward of the fused-recurrent op (absent in the reference: fused_recurrent_palimpsa.py:250-253). */
 int palimpsa_recurrent_bwd(const palimpsa_bwd_params *params, void *cuda_stream);
 

@@ -58,6 +58,7 @@ SYMBOLS = {
     "palimpsa_decode_step": (C.c_int, [C.POINTER(FwdParams), C.c_void_p]),
     "palimpsa_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(Problem)]),
     "palimpsa_chunk_bwd": (C.c_int, [C.POINTER(BwdParams), C.c_void_p]),
+    "palimpsa_chunk_bwd_stages": (C.c_int, [C.POINTER(BwdParams), C.c_void_p, C.c_int]),
     "palimpsa_recurrent_bwd": (C.c_int, [C.POINTER(BwdParams), C.c_void_p]),
 }
 

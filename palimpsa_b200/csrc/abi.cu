@@ -125,13 +125,20 @@ size_t palimpsa_bwd_workspace_bytes(const palimpsa_problem* p) {
 int palimpsa_chunk_bwd(const palimpsa_bwd_params* prm, void* cuda_stream) {
     int rc = check_bwd(prm);
     if (rc) return rc;
-    return launch_bwd(prm, static_cast<cudaStream_t>(cuda_stream));
+    return launch_bwd(prm, static_cast<cudaStream_t>(cuda_stream), 3);
+}
+
+int palimpsa_chunk_bwd_stages(const palimpsa_bwd_params* prm, void* cuda_stream, int stages) {
+    int rc = check_bwd(prm);
+    if (rc) return rc;
+    if (stages < 1 || stages > 3) return PALIMPSA_E_SHAPE;
+    return launch_bwd(prm, static_cast<cudaStream_t>(cuda_stream), stages);
 }
 
 int palimpsa_recurrent_bwd(const palimpsa_bwd_params* prm, void* cuda_stream) {
     int rc = check_bwd(prm);
     if (rc) return rc;
-    return launch_bwd(prm, static_cast<cudaStream_t>(cuda_stream));
+    return launch_bwd(prm, static_cast<cudaStream_t>(cuda_stream), 3);
 }
 
 }  // extern "C"

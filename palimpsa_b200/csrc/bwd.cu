@@ -693,7 +693,7 @@ static int launch_bwd_t(const BwdArgs& a, int tiles, cudaStream_t stream) {
 
 static bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
 
-int launch_bwd(const palimpsa_bwd_params* prm, cudaStream_t stream) {
+int launch_bwd(const palimpsa_bwd_params* prm, cudaStream_t stream, int stages) {
     const palimpsa_problem& p = prm->p;
     const BwdWorkspace ws = bwd_workspace_layout(p);
     if (!ws.tiles) return PALIMPSA_E_DIM;
@@ -715,8 +715,8 @@ int launch_bwd(const palimpsa_bwd_params* prm, cudaStream_t stream) {
     a.aligned = ((p.K * es) % 16 == 0) && ((p.V * es) % 16 == 0) && aligned16(p.q) && aligned16(p.k) &&
                 aligned16(p.v) && aligned16(p.b) && aligned16(prm->d_o) &&
                 (a.d_o_var == nullptr || aligned16(a.d_o_var)) && ((reinterpret_cast<uintptr_t>(p.gt) & 3) == 0);
-    int rc;
-    switch (ws.KP) {
+    int rc = PALIMPSA_OK;
+    if (stages & 1) switch (ws.KP) {
         case 16: rc = launch_bwd_t<2, 8, 2>(a, ws.tiles, stream); break;
         case 32: rc = launch_bwd_t<4, 8, 2>(a, ws.tiles, stream); break;
         case 48: rc = launch_bwd_t<6, 8, 2>(a, ws.tiles, stream); break;
@@ -728,6 +728,7 @@ int launch_bwd(const palimpsa_bwd_params* prm, cudaStream_t stream) {
         default: return PALIMPSA_E_DIM;
     }
     if (rc != PALIMPSA_OK) return rc;
+    if (!(stages & 2)) return PALIMPSA_OK;
     const long long rows = a.rows_total;
     if (rows > 0) {
         const int wpb = 8;

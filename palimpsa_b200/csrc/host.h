@@ -10,8 +10,8 @@ namespace palimpsa {
 // Enqueue the forward kernel (fwd.cu).  Parameters are assumed validated.
 int launch_fwd(const palimpsa_fwd_params* prm, cudaStream_t stream);
 
-// Backward (bwd.cu): main kernel + the two finishing kernels.
-int launch_bwd(const palimpsa_bwd_params* prm, cudaStream_t stream);
+// Backward (bwd.cu): main kernel (stages bit 0) + the two finishing kernels (bit 1).
+int launch_bwd(const palimpsa_bwd_params* prm, cudaStream_t stream, int stages);
 
 // State rows (d_v) one backward CTA owns for this problem; the number of row tiles follows.
 int bwd_tile_rows(const palimpsa_problem& p);

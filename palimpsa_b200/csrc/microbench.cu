@@ -49,7 +49,7 @@ __global__ void k_rcp(float* sink, int iters) {
     for (int i = 0; i < CH; ++i) a[i] = 1.5f + threadIdx.x * 1e-3f + i;
     for (int it = 0; it < iters; ++it) {
 #pragma unroll
-        for (int i = 0; i < CH; ++i) a[i] = rcpa(a[i]);
+        for (int i = 0; i < CH; ++i) a[i] = rcpa(a[i] + 0.25f);  // the add keeps the chain from collapsing
     }
     float s = 0.f;
 #pragma unroll
@@ -96,6 +96,7 @@ extern "C" int palimpsa_microbench(int kind, int blocks, int iters, int reps, fl
             case 2: k_rcp<<<blocks, 256>>>(sink, iters); break;
             default: k_fwd_mix<<<blocks, 256>>>(sink, iters); break;
         }
+        if (cudaGetLastError() != cudaSuccess) return -3;
         cudaEventRecord(e1);
         if (cudaEventSynchronize(e1) != cudaSuccess) return -2;
         float t;
