@@ -63,6 +63,7 @@ extern "C" {
 
 #define PALIMPSA_MAX_K 256
 #define PALIMPSA_CKPT_INTERVAL 16   /* tokens between saved (M, I) checkpoints */
+#define PALIMPSA_STATIC_SCRATCH_BYTES (64u << 20) /* capacity of palimpsa_chunk_bwd_static */
 
 /* Problem description shared by forward and backward. */
 typedef struct palimpsa_problem {
@@ -148,6 +149,23 @@ int palimpsa_chunk_bwd(const palimpsa_bwd_params *params, void *cuda_stream);
  * overlap the two; stages == 3 equals palimpsa_chunk_bwd.  No counterpart in the reference, whose
  * backward is one kernel plus torch reductions (chunk_palimpsa_forgetting_scalar.py:592-613). */
 int palimpsa_chunk_bwd_stages(const palimpsa_bwd_params *params, void *cuda_stream, int stages);
+
+/* Backward for callers that must not allocate device memory: plugin hosts whose memory pool is
+ * fixed at start-up, real-time or interrupt-style service threads, and code running where
+ * cudaMalloc is unavailable or would stall the device (it synchronises).  Identical to
+ * palimpsa_chunk_bwd, except that params->workspace / workspace_bytes are ignored: the scratch is a
+ * fixed PALIMPSA_STATIC_SCRATCH_BYTES (64 MiB) array inside the library, resident on every GPU that
+ * loads the library for as long as the process lives.  The caller still passes every input and
+ * output buffer.  It calls no cudaMalloc, cudaFree or any allocating routine.
+ *   - Problems whose palimpsa_bwd_workspace_bytes() exceeds the capacity return PALIMPSA_E_LIMIT
+ *     (at d_k = d_v = 128 the capacity covers about 8000 (token, head) rows).
+ *   - The first call on each device looks up the array's device address (once per device, with that
+ *     device current); make that first call outside any stream capture.
+ *   - All calls share the one array, which keeps whatever the previous call left in it.  Nothing in
+ *     it has to start at zero: each call's main kernel writes every byte its finishing kernels read.
+ *     Two calls that overlap on the GPU (different streams, or threads) race on it; serialise them.
+ * This entry point has no counterpart in the reference. */
+int palimpsa_chunk_bwd_static(const palimpsa_bwd_params *params, void *cuda_stream);
 
 /* Backward of the fused-recurrent op (absent in the reference: fused_recurrent_palimpsa.py:250-253). */
 int palimpsa_recurrent_bwd(const palimpsa_bwd_params *params, void *cuda_stream);

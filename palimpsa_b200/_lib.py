@@ -12,6 +12,7 @@ F32, BF16, F16 = 0, 1, 2
 FLAG_UNCERTAINTY = 1
 FLAG_EXPLICIT_INIT = 2
 CKPT_INTERVAL = 16
+STATIC_SCRATCH_BYTES = 64 << 20
 
 
 class Problem(C.Structure):
@@ -59,6 +60,7 @@ SYMBOLS = {
     "palimpsa_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(Problem)]),
     "palimpsa_chunk_bwd": (C.c_int, [C.POINTER(BwdParams), C.c_void_p]),
     "palimpsa_chunk_bwd_stages": (C.c_int, [C.POINTER(BwdParams), C.c_void_p, C.c_int]),
+    "palimpsa_chunk_bwd_static": (C.c_int, [C.POINTER(BwdParams), C.c_void_p]),
     "palimpsa_recurrent_bwd": (C.c_int, [C.POINTER(BwdParams), C.c_void_p]),
 }
 

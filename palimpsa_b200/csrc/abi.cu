@@ -40,7 +40,7 @@ int check_fwd(const palimpsa_fwd_params* prm) {
     return PALIMPSA_OK;
 }
 
-int check_bwd(const palimpsa_bwd_params* prm) {
+int check_bwd(const palimpsa_bwd_params* prm, bool caller_workspace = true) {
     if (!prm) return PALIMPSA_E_NULL;
     if (prm->struct_size != sizeof(palimpsa_bwd_params)) return PALIMPSA_E_VERSION;
     int rc = check_problem(prm->p);
@@ -55,6 +55,7 @@ int check_bwd(const palimpsa_bwd_params* prm) {
     if (misaligned16(prm->ckpt_M) || misaligned16(prm->ckpt_I)) return PALIMPSA_E_ALIGN;
     const size_t need = palimpsa_bwd_workspace_bytes(&p);
     if (need == 0) return PALIMPSA_E_DIM;
+    if (!caller_workspace) return PALIMPSA_OK;
     if (!prm->workspace || prm->workspace_bytes < need) return PALIMPSA_E_WORKSPACE;
     if (reinterpret_cast<uintptr_t>(prm->workspace) & 255) return PALIMPSA_E_WORKSPACE;
     return PALIMPSA_OK;
@@ -133,6 +134,12 @@ int palimpsa_chunk_bwd_stages(const palimpsa_bwd_params* prm, void* cuda_stream,
     if (rc) return rc;
     if (stages < 1 || stages > 3) return PALIMPSA_E_SHAPE;
     return launch_bwd(prm, static_cast<cudaStream_t>(cuda_stream), stages);
+}
+
+int palimpsa_chunk_bwd_static(const palimpsa_bwd_params* prm, void* cuda_stream) {
+    int rc = check_bwd(prm, false);
+    if (rc) return rc;
+    return launch_bwd_static(prm, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int palimpsa_recurrent_bwd(const palimpsa_bwd_params* prm, void* cuda_stream) {

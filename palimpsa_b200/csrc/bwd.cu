@@ -20,6 +20,8 @@
 //
 // Finishing kernels: (1) per (token, head) row: sum the row tiles, cast dq/dk, form
 // dgt = -g f df and the per-row terms of dg and dIp; (2) per head: ordered sum over rows.
+#include <mutex>
+
 #include "common.cuh"
 #include "host.h"
 
@@ -741,6 +743,38 @@ int launch_bwd(const palimpsa_bwd_params* prm, cudaStream_t stream, int stages) 
                                               reinterpret_cast<float*>(base + ws.w_dip), prm->dg, prm->dIp,
                                               p.total_tokens, p.H);
     return cudaGetLastError() == cudaSuccess ? PALIMPSA_OK : PALIMPSA_E_LAUNCH;
+}
+
+// ---- backward with library-owned scratch -----------------------------------------------------------
+// For callers that cannot allocate device memory themselves: the partial-sum scratch of the backward
+// lives in this fixed array instead of a caller-provided workspace.  Every CUDA context that loads the
+// library carries the array until it exits.  Host code may not use the array's name as an address; the
+// device address is looked up once per device below.
+static __device__ __align__(256) unsigned char g_static_scratch[PALIMPSA_STATIC_SCRATCH_BYTES];
+
+int launch_bwd_static(const palimpsa_bwd_params* prm, cudaStream_t stream) {
+    constexpr int MAX_DEV = 64;
+    static void* addr[MAX_DEV] = {};
+    static std::mutex mu;
+    const BwdWorkspace ws = bwd_workspace_layout(prm->p);
+    if (!ws.tiles) return PALIMPSA_E_DIM;
+    if (ws.total > (size_t)PALIMPSA_STATIC_SCRATCH_BYTES) return PALIMPSA_E_LIMIT;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return PALIMPSA_E_LAUNCH;
+    void* ptr = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!addr[dev]) {
+            void* sym = nullptr;
+            if (cudaGetSymbolAddress(&sym, g_static_scratch) != cudaSuccess || !sym) return PALIMPSA_E_LAUNCH;
+            addr[dev] = sym;
+        }
+        ptr = addr[dev];
+    }
+    palimpsa_bwd_params local = *prm;
+    local.workspace = ptr;
+    local.workspace_bytes = PALIMPSA_STATIC_SCRATCH_BYTES;
+    return launch_bwd(&local, stream, 3);
 }
 
 }  // namespace palimpsa

@@ -13,6 +13,9 @@ int launch_fwd(const palimpsa_fwd_params* prm, cudaStream_t stream);
 // Backward (bwd.cu): main kernel (stages bit 0) + the two finishing kernels (bit 1).
 int launch_bwd(const palimpsa_bwd_params* prm, cudaStream_t stream, int stages);
 
+// Backward whose scratch is the library's own fixed device array (bwd.cu).
+int launch_bwd_static(const palimpsa_bwd_params* prm, cudaStream_t stream);
+
 // State rows (d_v) one backward CTA owns for this problem; the number of row tiles follows.
 int bwd_tile_rows(const palimpsa_problem& p);
 
