@@ -342,13 +342,14 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile-batch", type=int, default=4, help="batch size of --profile-case")
     ap.add_argument("--profile-case", action="store_true",
                     help="run a few forward+backward steps of a half-size batch (B=4) and exit: the small case "
                          "that profiler captures are taken on")
     args = ap.parse_args()
     if args.profile_case:
         dev = torch.device("cuda", 0)
-        _, d = make_inputs(4, C2["T"], C2["H"], C2["K"], C2["V"], torch.bfloat16, dev)
+        _, d = make_inputs(args.profile_batch, C2["T"], C2["H"], C2["K"], C2["V"], torch.bfloat16, dev)
         for _ in range(3):
             fwd_bwd(d)
         torch.cuda.synchronize()

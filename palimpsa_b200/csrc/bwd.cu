@@ -20,6 +20,7 @@
 //
 // Finishing kernels: (1) per (token, head) row: sum the row tiles, cast dq/dk, form
 // dgt = -g f df and the per-row terms of dg and dIp; (2) per head: ordered sum over rows.
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -42,12 +43,15 @@ struct BwdArgs {
 };
 
 struct BwdSmem {
-    int ks, qs, qqs, vs, bs, dys, dyvs, fcn, dvs, dbs, wred, slots, ckb, kred;
+    int ks, qs, qqs, vs2, bs2, dys2, dyvs2, fc2, fn2, dvs, dbs, wred, slots, ckb, kred;
     int ck_stage;  // bytes of one (M, I) checkpoint stage
-    int raw, rq, rk, rv, rb, rdo, rdov, rgt, raw_stage;
+    int raw, rq, rk, rv, rb, rdo, rdov, rgt;
     int total;
 };
 
+// Shared-memory plan of one backward CTA (KP padded d_k, TV state rows, NE state elements per thread,
+// WV row groups).  Operand tiles v, b, dy are stored with every value duplicated ({x, x}) so that a
+// 64-bit load yields the register pair the packed FP32 instructions want.
 __host__ __device__ inline BwdSmem bwd_smem_layout(int KP, int TV, int NE, int nthr, int WV, int es, bool unc) {
     BwdSmem s;
     int off = 0;
@@ -59,18 +63,19 @@ __host__ __device__ inline BwdSmem bwd_smem_layout(int KP, int TV, int NE, int n
     s.ks = take(TB * KP * 4);
     s.qs = take(TB * KP * 4);
     s.qqs = unc ? take(TB * KP * 4) : 0;
-    s.vs = take(TB * TV * 4);
-    s.bs = take(TB * TV * 4);
-    s.dys = take(TB * TV * 4);
-    s.dyvs = unc ? take(TB * TV * 4) : 0;
-    s.fcn = take(TB * 16);
+    s.vs2 = take(TB * TV * 8);
+    s.bs2 = take(TB * TV * 8);
+    s.dys2 = take(TB * TV * 8);
+    s.dyvs2 = unc ? take(TB * TV * 8) : 0;
+    s.fc2 = take(TB * 16);
+    s.fn2 = take(TB * 8);
     s.dvs = take(TB * TV * 4);
     s.dbs = take(TB * TV * 4);
     s.wred = take((nthr / 32) * TB * 2 * 4);
     s.slots = take(2 * 2 * NE * nthr * 4);
     s.ck_stage = 2 * TV * KP * 4;
     s.ckb = take(2 * s.ck_stage);
-    s.kred = take(GR * WV * (unc ? 4 : 3) * KP * 4);
+    s.kred = take(GR * WV * 2 * KP * 4);
     s.raw = off;
     int r = 0;
     auto rtake = [&](int bytes) {
@@ -85,29 +90,30 @@ __host__ __device__ inline BwdSmem bwd_smem_layout(int KP, int TV, int NE, int n
     s.rdo = rtake(TB * TV * es);
     s.rdov = unc ? rtake(TB * TV * es) : 0;
     s.rgt = rtake((TB + 1) * 4);
-    s.raw_stage = r;
-    s.total = off + 2 * r;
+    s.total = off + r;
     return s;
 }
 
-// Asynchronous copies for one block: checkpoint rows always, raw inputs on the aligned path.
-__device__ __forceinline__ void bwd_issue(const BwdArgs& a, unsigned char* sm, const BwdSmem& L, int stage_idx, int es,
-                                          int KP, int TV, long long tok0, int nt, int nt_ext, long long slot, int h,
-                                          int v0, int tvw) {
+// Asynchronous copy of one block's checkpoint rows (M, I) into checkpoint stage `stage_idx`.
+__device__ __forceinline__ void bwd_issue_ckpt(const BwdArgs& a, unsigned char* sm, const BwdSmem& L, int stage_idx,
+                                               int KP, int TV, long long slot, int h, int v0, int tvw) {
     const palimpsa_problem& p = a.p;
     const int nthr = blockDim.x, tid = threadIdx.x;
-    // checkpoint (M, I): tvw rows of KP floats
-    {
-        unsigned char* ck = sm + L.ckb + stage_idx * L.ck_stage;
-        const int cr = KP / 4;
-        const long long base = ((slot * p.H + h) * (long long)p.V + v0) * KP;
-        for (int i = tid; i < tvw * cr; i += nthr) {
-            cp_async16(ck + i * 16, a.ckpt_M + base + (long long)i * 4);
-            cp_async16(ck + TV * KP * 4 + i * 16, a.ckpt_I + base + (long long)i * 4);
-        }
+    unsigned char* ck = sm + L.ckb + stage_idx * L.ck_stage;
+    const int cr = KP / 4;
+    const long long base = ((slot * p.H + h) * (long long)p.V + v0) * KP;
+    for (int i = tid; i < tvw * cr; i += nthr) {
+        cp_async16(ck + i * 16, a.ckpt_M + base + (long long)i * 4);
+        cp_async16(ck + TV * KP * 4 + i * 16, a.ckpt_I + base + (long long)i * 4);
     }
-    if (!a.aligned) return;
-    unsigned char* stage = sm + L.raw + stage_idx * L.raw_stage;
+}
+
+// Asynchronous copy of one block's raw inputs (aligned path only).
+__device__ __forceinline__ void bwd_issue_raw(const BwdArgs& a, unsigned char* sm, const BwdSmem& L, int es, int KP,
+                                              int TV, long long tok0, int nt, int nt_ext, int h, int v0, int tvw) {
+    const palimpsa_problem& p = a.p;
+    const int nthr = blockDim.x, tid = threadIdx.x;
+    unsigned char* stage = sm + L.raw;
     const int cq = p.K * es / 16;
     const char* gq = reinterpret_cast<const char*>(p.q);
     const char* gk = reinterpret_cast<const char*>(p.k);
@@ -136,12 +142,12 @@ __device__ __forceinline__ void bwd_issue(const BwdArgs& a, unsigned char* sm, c
 }
 
 template <int DT, bool ALIGNED, bool UNC>
-__device__ __forceinline__ void bwd_convert(const BwdArgs& a, unsigned char* sm, const unsigned char* stage,
-                                            const BwdSmem& L, int KP, int TV, long long tok0, int nt, int nt_ext,
-                                            int h, int v0, float gh, float iph) {
+__device__ __forceinline__ void bwd_convert(const BwdArgs& a, unsigned char* sm, const BwdSmem& L, int KP, int TV,
+                                            long long tok0, int nt, int nt_ext, int h, int v0, float gh, float iph) {
     const palimpsa_problem& p = a.p;
     const int nthr = blockDim.x, tid = threadIdx.x;
     const int K4 = KP / 4, V4 = TV / 4;
+    const unsigned char* stage = sm + L.raw;
     float4* qs = reinterpret_cast<float4*>(sm + L.qs);
     float4* ks = reinterpret_cast<float4*>(sm + L.ks);
     float4* qqs = reinterpret_cast<float4*>(sm + L.qqs);
@@ -163,10 +169,10 @@ __device__ __forceinline__ void bwd_convert(const BwdArgs& a, unsigned char* sm,
         ks[i] = kv;
         if (UNC) qqs[i] = make_float4(sc * qv.x * qv.x, sc * qv.y * qv.y, sc * qv.z * qv.z, sc * qv.w * qv.w);
     }
-    float4* vs = reinterpret_cast<float4*>(sm + L.vs);
-    float4* bs = reinterpret_cast<float4*>(sm + L.bs);
-    float4* dys = reinterpret_cast<float4*>(sm + L.dys);
-    float4* dyvs = reinterpret_cast<float4*>(sm + L.dyvs);
+    float4* vs = reinterpret_cast<float4*>(sm + L.vs2);
+    float4* bs = reinterpret_cast<float4*>(sm + L.bs2);
+    float4* dys = reinterpret_cast<float4*>(sm + L.dys2);
+    float4* dyvs = reinterpret_cast<float4*>(sm + L.dyvs2);
     for (int i = tid; i < TB * V4; i += nthr) {
         int t = i / V4, c4 = i - t * V4;
         float4 vv = make_float4(0.f, 0.f, 0.f, 0.f), bv = vv, dv = vv, dvv = vv;
@@ -184,13 +190,14 @@ __device__ __forceinline__ void bwd_convert(const BwdArgs& a, unsigned char* sm,
                 if (UNC) dvv = ld4_guarded<DT>(a.d_o_var, row + v0 + c4 * 4, row + p.V);
             }
         }
-        vs[i] = vv;
-        bs[i] = bv;
-        dys[i] = dv;
-        if (UNC) dyvs[i] = dvv;
+        st_dup4(vs, i, vv);
+        st_dup4(bs, i, bv);
+        st_dup4(dys, i, dv);
+        if (UNC) st_dup4(dyvs, i, dvv);
     }
-    // per token: f, c = (1-f)*Ip, f of the NEXT token of the sequence (0 past its end), gt
-    float4* fcn = reinterpret_cast<float4*>(sm + L.fcn);
+    // per token: {f, f, c, c} with c = (1-f)*Ip, and {fn, fn}: f of the NEXT token of the sequence (0 past its end)
+    float4* fc2 = reinterpret_cast<float4*>(sm + L.fc2);
+    float2* fn2 = reinterpret_cast<float2*>(sm + L.fn2);
     for (int i = tid; i < TB; i += nthr) {
         float g0 = 0.f, g1 = 0.f;
         const bool has0 = i < nt, has1 = i + 1 < nt_ext;
@@ -204,7 +211,9 @@ __device__ __forceinline__ void bwd_convert(const BwdArgs& a, unsigned char* sm,
         }
         const float f = expf(-g0 * gh);
         const float fn = has1 ? expf(-g1 * gh) : 0.f;
-        fcn[i] = make_float4(f, (1.f - f) * iph, fn, g0);
+        const float c = (1.f - f) * iph;
+        fc2[i] = make_float4(f, f, c, c);
+        fn2[i] = make_float2(fn, fn);
     }
 }
 
@@ -213,13 +222,16 @@ struct State {
     float2 M[RV][NP], I[RV][NP];
 };
 
-template <int RK, int KG, int RV, bool UNC>
-__global__ void __launch_bounds__(256) bwd_kernel(const BwdArgs a) {
-    constexpr int KP = RK * KG, VG = 32 / KG, NP = RK / 2, NE = RV * RK, NQ = UNC ? 4 : 3, KP2 = KP / 2;
+template <int RK, int KG, int RV, int W, bool UNC>
+__global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
+    constexpr int KP = RK * KG, VG = 32 / KG, NP = RK / 2, NE = RV * RK, KP2 = KP / 2;
+    constexpr int TV = W * VG * RV, WV = W * VG, NTHR = 32 * W;
+    constexpr int NG = TB / GR;       // groups per block
+    constexpr int NR1 = GR * RV * 2;  // per-group d_v-indexed partials of a thread: (token, row, dv|db)
+    constexpr int NR2 = GR * 2;       // per-group per-token scalars: (token, df|sum GI)
     extern __shared__ __align__(16) unsigned char sm[];
     const palimpsa_problem& p = a.p;
-    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, nthr = blockDim.x, W = nthr >> 5;
-    const int TV = W * VG * RV, WV = W * VG;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int kg = lane % KG, vg = lane / KG, wv = w * VG + vg;
     const int row0 = wv * RV;
     const int n = blockIdx.y / p.H, h = blockIdx.y - n * p.H;
@@ -227,7 +239,7 @@ __global__ void __launch_bounds__(256) bwd_kernel(const BwdArgs a) {
     const int v0 = tile * TV;
     const int tvw = min(TV, p.V - v0);
     const int es = dtype_size(p.io_dtype);
-    const BwdSmem L = bwd_smem_layout(KP, TV, NE, nthr, WV, es, UNC);
+    const BwdSmem L = bwd_smem_layout(KP, TV, NE, NTHR, WV, es, UNC);
     int bos, len;
     seq_range(p, n, bos, len);
     if (len <= 0) return;
@@ -237,18 +249,20 @@ __global__ void __launch_bounds__(256) bwd_kernel(const BwdArgs a) {
     const int nblk = (len + TB - 1) / TB;
     const bool has_init = p.init_mu != nullptr || (p.flags & PALIMPSA_FLAG_EXPLICIT_INIT);
 
-    const float2* ks2 = reinterpret_cast<const float2*>(sm + L.ks);
-    const float2* qs2 = reinterpret_cast<const float2*>(sm + L.qs);
-    const float2* qqs2 = reinterpret_cast<const float2*>(sm + L.qqs);
-    const float* vs = reinterpret_cast<const float*>(sm + L.vs);
-    const float* bs = reinterpret_cast<const float*>(sm + L.bs);
-    const float* dys = reinterpret_cast<const float*>(sm + L.dys);
-    const float* dyvs = reinterpret_cast<const float*>(sm + L.dyvs);
-    const float4* fcn = reinterpret_cast<const float4*>(sm + L.fcn);
+    // this thread's d_k columns are RK*kg .. RK*kg+RK-1: pair q covers columns RK*kg + 2q, +1
+    const float2* ks2 = reinterpret_cast<const float2*>(sm + L.ks) + NP * kg;
+    const float2* qs2 = reinterpret_cast<const float2*>(sm + L.qs) + NP * kg;
+    const float2* qqs2 = reinterpret_cast<const float2*>(sm + L.qqs) + NP * kg;
+    const float2* vs2 = reinterpret_cast<const float2*>(sm + L.vs2) + row0;
+    const float2* bs2 = reinterpret_cast<const float2*>(sm + L.bs2) + row0;
+    const float2* dys2 = reinterpret_cast<const float2*>(sm + L.dys2) + row0;
+    const float2* dyvs2 = reinterpret_cast<const float2*>(sm + L.dyvs2) + row0;
+    const float4* fc2 = reinterpret_cast<const float4*>(sm + L.fc2);
+    const float2* fn2 = reinterpret_cast<const float2*>(sm + L.fn2);
     float* dvs = reinterpret_cast<float*>(sm + L.dvs);
     float* dbs = reinterpret_cast<float*>(sm + L.dbs);
     float* wred = reinterpret_cast<float*>(sm + L.wred);
-    float* slots = reinterpret_cast<float*>(sm + L.slots);
+    float4* slots4 = reinterpret_cast<float4*>(sm + L.slots) + tid;
     float2* kred2 = reinterpret_cast<float2*>(sm + L.kred);
 
     // running state gradients: GM = dL/dM_t, nGI = -dL/dI_t of the earliest token processed so far
@@ -266,25 +280,44 @@ __global__ void __launch_bounds__(256) bwd_kernel(const BwdArgs a) {
             const bool ok = row0 + r < tvw;
 #pragma unroll
             for (int q = 0; q < NP; ++q) {
-                const int e = (row0 + r) * KP + 2 * (q * KG + kg);
+                const int e = (row0 + r) * KP + RK * kg + 2 * q;
                 s.M[r][q] = ok ? *reinterpret_cast<const float2*>(ckM + e) : make_float2(0.f, 0.f);
                 s.I[r][q] = ok ? *reinterpret_cast<const float2*>(ckI + e) : make_float2(1.f, 1.f);
             }
         }
     };
+    auto load_slot = [&](State<RV, NP>& s, int slot) {
+        const float4* sl = slots4 + slot * (NE / 2) * NTHR;
+#pragma unroll
+        for (int r = 0; r < RV; ++r)
+#pragma unroll
+            for (int q = 0; q < NP; ++q) {
+                const float4 x = sl[(r * NP + q) * NTHR];
+                s.M[r][q] = make_float2(x.x, x.y);
+                s.I[r][q] = make_float2(x.z, x.w);
+            }
+    };
+    auto store_slot = [&](const State<RV, NP>& s, int slot) {
+        float4* sl = slots4 + slot * (NE / 2) * NTHR;
+#pragma unroll
+        for (int r = 0; r < RV; ++r)
+#pragma unroll
+            for (int q = 0; q < NP; ++q)
+                sl[(r * NP + q) * NTHR] = make_float4(s.M[r][q].x, s.M[r][q].y, s.I[r][q].x, s.I[r][q].y);
+    };
     // one forward step of the recurrence on token tl of the staged block
     auto fstep = [&](State<RV, NP>& s, int tl) {
-        const float4 fv = fcn[tl];
-        const float2 ff = dup2(fv.x), cc = dup2(fv.y);
+        const float4 fv = fc2[tl];
+        const float2 ff = make_float2(fv.x, fv.y), cc = make_float2(fv.z, fv.w);
         float2 vr[RV], br[RV];
 #pragma unroll
         for (int r = 0; r < RV; ++r) {
-            vr[r] = dup2(vs[tl * TV + row0 + r]);
-            br[r] = dup2(bs[tl * TV + row0 + r]);
+            vr[r] = vs2[tl * TV + r];
+            br[r] = bs2[tl * TV + r];
         }
 #pragma unroll
         for (int q = 0; q < NP; ++q) {
-            const float2 kp = ks2[tl * KP2 + q * KG + kg];
+            const float2 kp = ks2[tl * KP2 + q];
             const float2 kk = fmul2(kp, kp);
 #pragma unroll
             for (int r = 0; r < RV; ++r) {
@@ -297,8 +330,8 @@ __global__ void __launch_bounds__(256) bwd_kernel(const BwdArgs a) {
     {
         const int c = nblk - 1;
         const int nt = min(TB, len - c * TB);
-        bwd_issue(a, sm, L, 0, es, KP, TV, (long long)bos + c * TB, nt, min(TB + 1, len - c * TB), slot0 + c, h, v0,
-                  tvw);
+        bwd_issue_ckpt(a, sm, L, 0, KP, TV, slot0 + c, h, v0, tvw);
+        if (a.aligned) bwd_issue_raw(a, sm, L, es, KP, TV, (long long)bos + c * TB, nt, nt, h, v0, tvw);
         cp_async_commit();
     }
 
@@ -309,204 +342,162 @@ __global__ void __launch_bounds__(256) bwd_kernel(const BwdArgs a) {
         const int nt_ext = min(TB + 1, len - t0);
         const long long tok0 = (long long)bos + t0;
         const int st = it & 1;
+        cp_async_wait<0>();
+        __syncthreads();
+        if (a.aligned) {
+            if (p.io_dtype == PALIMPSA_BF16)
+                bwd_convert<PALIMPSA_BF16, true, UNC>(a, sm, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
+            else if (p.io_dtype == PALIMPSA_F32)
+                bwd_convert<PALIMPSA_F32, true, UNC>(a, sm, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
+            else
+                bwd_convert<PALIMPSA_F16, true, UNC>(a, sm, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
+        } else {
+            if (p.io_dtype == PALIMPSA_BF16)
+                bwd_convert<PALIMPSA_BF16, false, UNC>(a, sm, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
+            else if (p.io_dtype == PALIMPSA_F32)
+                bwd_convert<PALIMPSA_F32, false, UNC>(a, sm, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
+            else
+                bwd_convert<PALIMPSA_F16, false, UNC>(a, sm, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
+        }
+        __syncthreads();
+        // the raw stage is free again: fetch the next (earlier) block while this one is processed
         if (c > 0) {
             const int t0n = t0 - TB;
-            bwd_issue(a, sm, L, st ^ 1, es, KP, TV, (long long)bos + t0n, TB, min(TB + 1, len - t0n), slot0 + c - 1, h,
-                      v0, tvw);
+            bwd_issue_ckpt(a, sm, L, st ^ 1, KP, TV, slot0 + c - 1, h, v0, tvw);
+            if (a.aligned)
+                bwd_issue_raw(a, sm, L, es, KP, TV, (long long)bos + t0n, TB, min(TB + 1, len - t0n), h, v0, tvw);
             cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
         }
-        __syncthreads();
-        {
-            const unsigned char* stage = sm + L.raw + st * L.raw_stage;
-            if (a.aligned) {
-                if (p.io_dtype == PALIMPSA_BF16)
-                    bwd_convert<PALIMPSA_BF16, true, UNC>(a, sm, stage, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
-                else if (p.io_dtype == PALIMPSA_F32)
-                    bwd_convert<PALIMPSA_F32, true, UNC>(a, sm, stage, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
-                else
-                    bwd_convert<PALIMPSA_F16, true, UNC>(a, sm, stage, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
-            } else {
-                if (p.io_dtype == PALIMPSA_BF16)
-                    bwd_convert<PALIMPSA_BF16, false, UNC>(a, sm, stage, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
-                else if (p.io_dtype == PALIMPSA_F32)
-                    bwd_convert<PALIMPSA_F32, false, UNC>(a, sm, stage, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
-                else
-                    bwd_convert<PALIMPSA_F16, false, UNC>(a, sm, stage, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
-            }
-        }
-        __syncthreads();
 
-        // ---- forward sweep: park the start state of groups 1 .. glast-1, keep glast's in registers
-        const int glast = (nt - 1) / GR;
+        // Tokens past the end of the sequence (last block only) were staged as identity steps (f = 1,
+        // all other operands 0): they leave the state and every gradient untouched, so the block is
+        // always processed as NG full groups with no per-token conditionals.
+        // ---- forward sweep: park the start states of groups 1 .. NG-2, keep the last group's in registers
         State<RV, NP> P[GR + 1];
         load_ck(P[0], st);
-        for (int t = 0; t < glast * GR; ++t) {
-            fstep(P[0], t);
-            if ((t & (GR - 1)) == GR - 1 && (t / GR) + 1 < glast) {
-                float* sl = slots + (size_t)(t / GR) * 2 * NE * nthr;
+#pragma unroll 1
+        for (int g = 0; g < NG - 1; ++g) {
 #pragma unroll
-                for (int r = 0; r < RV; ++r)
-#pragma unroll
-                    for (int q = 0; q < NP; ++q) {
-                        const int e = (r * NP + q) * 4;
-                        sl[(e + 0) * nthr + tid] = P[0].M[r][q].x;
-                        sl[(e + 1) * nthr + tid] = P[0].M[r][q].y;
-                        sl[(e + 2) * nthr + tid] = P[0].I[r][q].x;
-                        sl[(e + 3) * nthr + tid] = P[0].I[r][q].y;
-                    }
-            }
+            for (int j = 0; j < GR; ++j) fstep(P[0], g * GR + j);
+            if (g < NG - 2) store_slot(P[0], g);
         }
 
-        for (int gi = glast; gi >= 0; --gi) {
-            if (gi < glast) {
-                if (gi == 0) {
-                    load_ck(P[0], st);
-                } else {
-                    const float* sl = slots + (size_t)(gi - 1) * 2 * NE * nthr;
-#pragma unroll
-                    for (int r = 0; r < RV; ++r)
-#pragma unroll
-                        for (int q = 0; q < NP; ++q) {
-                            const int e = (r * NP + q) * 4;
-                            P[0].M[r][q] = make_float2(sl[(e + 0) * nthr + tid], sl[(e + 1) * nthr + tid]);
-                            P[0].I[r][q] = make_float2(sl[(e + 2) * nthr + tid], sl[(e + 3) * nthr + tid]);
-                        }
-                }
-            }
-            const int ng = min(GR, nt - gi * GR);
+#pragma unroll 1
+        for (int gi = NG - 1; gi >= 0; --gi) {
+            if (gi == 0)
+                load_ck(P[0], st);
+            else if (gi < NG - 1)
+                load_slot(P[0], gi - 1);
 #pragma unroll
             for (int j = 0; j < GR; ++j) {
-                if (j < ng) {
-                    P[j + 1] = P[j];
-                    fstep(P[j + 1], gi * GR + j);
-                }
+                P[j + 1] = P[j];
+                fstep(P[j + 1], gi * GR + j);
             }
+            float red1[NR1], red2[NR2];
             // ---- reverse walk over the group ----------------------------------------------------
 #pragma unroll
             for (int j = GR - 1; j >= 0; --j) {
-                if (j < ng) {
-                    const int tl = gi * GR + j;
-                    const float4 fv = fcn[tl];
-                    const float2 fn = dup2(fv.z);
-                    float2 dqs[NP], Ak[NP], Bk[NP], Uk[NP];
-                    float2 Sa = make_float2(0.f, 0.f), Sb = Sa, Sc = Sa;
+                const int tl = gi * GR + j;
+                const float2 fn = fn2[tl];
+                float2 dqs[NP], Ak[NP], Bk[NP], Uk[NP];
+                float2 Sa = make_float2(0.f, 0.f), Sb = Sa, Sc = Sa;
 #pragma unroll
-                    for (int q = 0; q < NP; ++q) dqs[q] = Ak[q] = Bk[q] = Uk[q] = make_float2(0.f, 0.f);
-                    float dvr[RV], dbr[RV];
-                    float2 kp[NP], kk[NP], qp[NP], qq[NP];
+                for (int q = 0; q < NP; ++q) dqs[q] = Ak[q] = Bk[q] = Uk[q] = make_float2(0.f, 0.f);
+                float2 kp[NP], kk[NP], qp[NP], qq[NP];
+#pragma unroll
+                for (int q = 0; q < NP; ++q) {
+                    kp[q] = ks2[tl * KP2 + q];
+                    kk[q] = fmul2(kp[q], kp[q]);
+                    qp[q] = qs2[tl * KP2 + q];
+                    qq[q] = UNC ? qqs2[tl * KP2 + q] : make_float2(0.f, 0.f);
+                }
+#pragma unroll
+                for (int r = 0; r < RV; ++r) {
+                    const float2 vv = vs2[tl * TV + r];
+                    const float2 bv = bs2[tl * TV + r];
+                    const float2 dy = dys2[tl * TV + r];
+                    const float2 dyv = UNC ? dyvs2[tl * TV + r] : make_float2(0.f, 0.f);
+                    float2 dva = make_float2(0.f, 0.f), dba = dva;
 #pragma unroll
                     for (int q = 0; q < NP; ++q) {
-                        kp[q] = ks2[tl * KP2 + q * KG + kg];
-                        kk[q] = fmul2(kp[q], kp[q]);
-                        qp[q] = qs2[tl * KP2 + q * KG + kg];
-                        qq[q] = UNC ? qqs2[tl * KP2 + q * KG + kg] : make_float2(0.f, 0.f);
+                        const float2 Mt = P[j + 1].M[r][q], It = P[j + 1].I[r][q];
+                        const float2 rr = rcp2(It);
+                        const float2 mu = fmul2(Mt, rr);
+                        const float2 hh = fmul2(fmul2(dy, qp[q]), rr);
+                        GM[r][q] = ffma2(fn, GM[r][q], hh);
+                        float2 hm = fmul2(hh, mu);
+                        if (UNC) hm = ffma2(fmul2(dyv, qq[q]), fmul2(rr, rr), hm);
+                        nGI[r][q] = ffma2(fn, nGI[r][q], hm);
+                        dqs[q] = ffma2(dy, mu, dqs[q]);
+                        if (UNC) Uk[q] = ffma2(dyv, rr, Uk[q]);
+                        Ak[q] = ffma2(GM[r][q], vv, Ak[q]);
+                        Bk[q] = ffma2(nGI[r][q], bv, Bk[q]);
+                        dva = ffma2(GM[r][q], kp[q], dva);
+                        dba = ffma2(nGI[r][q], kk[q], dba);
+                        Sa = ffma2(GM[r][q], P[j].M[r][q], Sa);
+                        Sb = ffma2(nGI[r][q], P[j].I[r][q], Sb);
+                        Sc = fadd2(Sc, nGI[r][q]);
                     }
+                    red1[(j * RV + r) * 2 + 0] = dva.x + dva.y;
+                    red1[(j * RV + r) * 2 + 1] = -(dba.x + dba.y);
+                }
+                // this row group's share of dq and dk for the token -> shared memory
+                {
+                    float2* dst = kred2 + ((j * WV + wv) * 2) * KP2 + NP * kg;
+                    const float2 sc2 = dup2(p.scale), m2 = dup2(-2.f);
 #pragma unroll
-                    for (int r = 0; r < RV; ++r) {
-                        const float2 vv = dup2(vs[tl * TV + row0 + r]);
-                        const float2 bv = dup2(bs[tl * TV + row0 + r]);
-                        const float2 dy = dup2(dys[tl * TV + row0 + r]);
-                        const float2 dyv = UNC ? dup2(dyvs[tl * TV + row0 + r]) : make_float2(0.f, 0.f);
-                        float2 dva = make_float2(0.f, 0.f), dba = dva;
-#pragma unroll
-                        for (int q = 0; q < NP; ++q) {
-                            const float2 Mt = P[j + 1].M[r][q], It = P[j + 1].I[r][q];
-                            const float2 rr = rcp2(It);
-                            const float2 mu = fmul2(Mt, rr);
-                            const float2 hh = fmul2(fmul2(dy, qp[q]), rr);
-                            GM[r][q] = ffma2(fn, GM[r][q], hh);
-                            float2 hm = fmul2(hh, mu);
-                            if (UNC) hm = ffma2(fmul2(dyv, qq[q]), fmul2(rr, rr), hm);
-                            nGI[r][q] = ffma2(fn, nGI[r][q], hm);
-                            dqs[q] = ffma2(dy, mu, dqs[q]);
-                            if (UNC) Uk[q] = ffma2(dyv, rr, Uk[q]);
-                            Ak[q] = ffma2(GM[r][q], vv, Ak[q]);
-                            Bk[q] = ffma2(nGI[r][q], bv, Bk[q]);
-                            dva = ffma2(GM[r][q], kp[q], dva);
-                            dba = ffma2(nGI[r][q], kk[q], dba);
-                            Sa = ffma2(GM[r][q], P[j].M[r][q], Sa);
-                            Sb = ffma2(nGI[r][q], P[j].I[r][q], Sb);
-                            Sc = fadd2(Sc, nGI[r][q]);
-                        }
-                        dvr[r] = dva.x + dva.y;
-                        dbr[r] = dba.x + dba.y;
+                    for (int q = 0; q < NP; ++q) {
+                        float2 dqv = fmul2(sc2, dqs[q]);
+                        if (UNC) dqv = ffma2(fmul2(dup2(2.f), qp[q]), Uk[q], dqv);
+                        dst[q] = dqv;
+                        dst[KP2 + q] = ffma2(fmul2(m2, kp[q]), Bk[q], Ak[q]);
                     }
-                    // d_k-indexed partial sums of this thread's rows -> shared memory
-                    {
-                        float2* dst = kred2 + ((size_t)(j * WV + wv) * NQ) * KP2;
+                }
+                const float sc_ = Sc.x + Sc.y;
+                red2[j * 2 + 0] = (Sa.x + Sa.y) - (Sb.x + Sb.y) + iph * sc_;
+                red2[j * 2 + 1] = -sc_;
+            }
+            // d_v-indexed sums over the KG lanes of a row; per-token scalars over the whole warp
+            xreduce<NR1, KG>(red1, lane);
+            {
+                constexpr int REM = NR1 >= KG ? NR1 / KG : 1;
+                const int base = xreduce_index<NR1, KG>(lane);
+                const bool owner = NR1 >= KG ? true : (kg & (KG / (NR1 < KG ? NR1 : KG) - 1)) == 0;
+                if (owner) {
 #pragma unroll
-                        for (int q = 0; q < NP; ++q) {
-                            const int pi = q * KG + kg;
-                            dst[0 * KP2 + pi] = dqs[q];
-                            dst[1 * KP2 + pi] = Ak[q];
-                            dst[2 * KP2 + pi] = Bk[q];
-                            if (UNC) dst[3 * KP2 + pi] = Uk[q];
-                        }
-                    }
-                    // d_v-indexed sums: reduce over the KG lanes of the row
-#pragma unroll
-                    for (int r = 0; r < RV; ++r) {
-                        float x = dvr[r], y = dbr[r];
-#pragma unroll
-                        for (int off = KG / 2; off >= 1; off >>= 1) {
-                            x += __shfl_xor_sync(0xffffffffu, x, off);
-                            y += __shfl_xor_sync(0xffffffffu, y, off);
-                        }
-                        if (kg == 0) {
-                            dvs[tl * TV + row0 + r] = x;
-                            dbs[tl * TV + row0 + r] = -y;
-                        }
-                    }
-                    // decay gradient and sum of GI: reduce over the warp
-                    {
-                        const float sc_ = Sc.x + Sc.y;
-                        float x = (Sa.x + Sa.y) - (Sb.x + Sb.y) + iph * sc_;
-                        float y = -sc_;
-#pragma unroll
-                        for (int off = 16; off >= 1; off >>= 1) {
-                            x += __shfl_xor_sync(0xffffffffu, x, off);
-                            y += __shfl_xor_sync(0xffffffffu, y, off);
-                        }
-                        if (lane == 0) {
-                            wred[(w * TB + tl) * 2 + 0] = x;
-                            wred[(w * TB + tl) * 2 + 1] = y;
-                        }
+                    for (int i = 0; i < REM; ++i) {
+                        const int id = base + i;
+                        const int j = id / (RV * 2), r = (id / 2) % RV, which = id & 1;
+                        (which ? dbs : dvs)[(gi * GR + j) * TV + row0 + r] = red1[i];
                     }
                 }
             }
+            xreduce<NR2, 32>(red2, lane);
+            if ((lane & (32 / NR2 - 1)) == 0) {
+                const int id = xreduce_index<NR2, 32>(lane);
+                wred[(w * TB + gi * GR + (id >> 1)) * 2 + (id & 1)] = red2[0];
+            }
             __syncthreads();
-            // ---- sum the row groups' d_k-indexed partials; emit this row tile's dq / dk --------------
-            for (int i = tid; i < ng * KP2; i += nthr) {
+            // ---- sum the row groups' shares; emit this row tile's dq / dk partials ----------------------
+            const int ng = min(GR, nt - gi * GR);  // tokens of the group that exist (<= 0 past the sequence end)
+            for (int i = tid; i < ng * KP2; i += NTHR) {
                 const int j = i / KP2, pi = i - j * KP2;
-                const int tl = gi * GR + j;
-                float2 s0 = make_float2(0.f, 0.f), s1 = s0, s2 = s0, s3 = s0;
+                const float2* src = kred2 + (j * WV * 2) * KP2 + pi;
+                float2 s0 = make_float2(0.f, 0.f), s1 = s0;
+#pragma unroll
                 for (int x = 0; x < WV; ++x) {
-                    const float2* src = kred2 + ((size_t)(j * WV + x) * NQ) * KP2 + pi;
-                    s0 = fadd2(s0, src[0]);
-                    s1 = fadd2(s1, src[KP2]);
-                    s2 = fadd2(s2, src[2 * KP2]);
-                    if (UNC) s3 = fadd2(s3, src[3 * KP2]);
+                    s0 = fadd2(s0, src[(x * 2) * KP2]);
+                    s1 = fadd2(s1, src[(x * 2 + 1) * KP2]);
                 }
-                const float2 kv = ks2[tl * KP2 + pi];
-                float2 dqv = make_float2(p.scale * s0.x, p.scale * s0.y);
-                if (UNC) {
-                    const float2 qv = qs2[tl * KP2 + pi];
-                    dqv.x += 2.f * qv.x * s3.x;
-                    dqv.y += 2.f * qv.y * s3.y;
-                }
-                const float2 dkv = make_float2(s1.x - 2.f * kv.x * s2.x, s1.y - 2.f * kv.y * s2.y);
-                const size_t e = (((size_t)tile * a.rows_total + (size_t)(tok0 + tl) * p.H + h) * KP2) + pi;
-                reinterpret_cast<float2*>(a.dq_part)[e] = dqv;
-                reinterpret_cast<float2*>(a.dk_part)[e] = dkv;
+                const size_t e = (((size_t)tile * a.rows_total + (size_t)(tok0 + gi * GR + j) * p.H + h) * KP2) + pi;
+                reinterpret_cast<float2*>(a.dq_part)[e] = s0;
+                reinterpret_cast<float2*>(a.dk_part)[e] = s1;
             }
             __syncthreads();
         }
 
         // ---- block epilogue: dv, db rows and the per-token scalars -----------------------------------
-        for (int i = tid; i < nt * TV; i += nthr) {
+        for (int i = tid; i < nt * TV; i += NTHR) {
             const int t = i / TV, r = i - t * TV;
             if (r < tvw) {
                 const long long e = ((tok0 + t) * p.H + h) * (long long)V + v0 + r;
@@ -516,11 +507,12 @@ __global__ void __launch_bounds__(256) bwd_kernel(const BwdArgs a) {
         }
         if (tid < nt) {
             float df = 0.f, s2 = 0.f;
+#pragma unroll
             for (int x = 0; x < W; ++x) {
                 df += wred[(x * TB + tid) * 2 + 0];
                 s2 += wred[(x * TB + tid) * 2 + 1];
             }
-            const float f = fcn[tid].x;
+            const float f = fc2[tid].x;
             float dip = (1.f - f) * s2;
             if (t0 + tid == 0 && !has_init) dip += f * s2;  // I_0 = Ip: the start-state gradient reaches Ip
             const size_t e = (size_t)tile * a.rows_total + (size_t)(tok0 + tid) * p.H + h;
@@ -631,6 +623,8 @@ static BwdConfig bwd_config(const palimpsa_problem& p) {
     const bool unc = (p.flags & PALIMPSA_FLAG_UNCERTAINTY) != 0;
     const int es = dtype_size(p.io_dtype);
     int W = (rpw == 1 || p.V > 4 * rpw) ? 8 : 4;
+    static const int force_w = [] { const char* e = getenv("PALIMPSA_BWD_WARPS"); return e ? atoi(e) : 0; }();
+    if (force_w == 4 && rpw > 1) W = 4;
     for (;;) {
         c.W = W;
         c.TV = W * rpw;
@@ -669,12 +663,10 @@ BwdWorkspace bwd_workspace_layout(const palimpsa_problem& p) {
     return ws;
 }
 
-template <int RK, int KG, int RV>
-static int launch_bwd_t(const BwdArgs& a, int tiles, cudaStream_t stream) {
-    constexpr int VG = 32 / KG;
+template <int RK, int KG, int RV, int W>
+static int launch_bwd_w(const BwdArgs& a, int tiles, cudaStream_t stream) {
+    constexpr int VG = 32 / KG, TV = W * VG * RV;
     const palimpsa_problem& p = a.p;
-    const BwdConfig cfg = bwd_config(p);
-    const int W = cfg.W, TV = cfg.TV;
     const bool unc = (p.flags & PALIMPSA_FLAG_UNCERTAINTY) != 0;
     const BwdSmem L = bwd_smem_layout(RK * KG, TV, RV * RK, 32 * W, W * VG, dtype_size(p.io_dtype), unc);
     if (L.total > 227 * 1024) return PALIMPSA_E_DIM;
@@ -682,15 +674,23 @@ static int launch_bwd_t(const BwdArgs& a, int tiles, cudaStream_t stream) {
     dim3 block(32 * W, 1, 1);
     cudaError_t e;
     if (unc) {
-        e = cudaFuncSetAttribute(bwd_kernel<RK, KG, RV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+        e = cudaFuncSetAttribute(bwd_kernel<RK, KG, RV, W, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
         if (e != cudaSuccess) return PALIMPSA_E_LAUNCH;
-        bwd_kernel<RK, KG, RV, true><<<grid, block, L.total, stream>>>(a);
+        bwd_kernel<RK, KG, RV, W, true><<<grid, block, L.total, stream>>>(a);
     } else {
-        e = cudaFuncSetAttribute(bwd_kernel<RK, KG, RV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+        e = cudaFuncSetAttribute(bwd_kernel<RK, KG, RV, W, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
         if (e != cudaSuccess) return PALIMPSA_E_LAUNCH;
-        bwd_kernel<RK, KG, RV, false><<<grid, block, L.total, stream>>>(a);
+        bwd_kernel<RK, KG, RV, W, false><<<grid, block, L.total, stream>>>(a);
     }
     return cudaGetLastError() == cudaSuccess ? PALIMPSA_OK : PALIMPSA_E_LAUNCH;
+}
+
+template <int RK, int KG, int RV>
+static int launch_bwd_t(const BwdArgs& a, int tiles, cudaStream_t stream) {
+    const BwdConfig cfg = bwd_config(a.p);
+    if (cfg.W == 8) return launch_bwd_w<RK, KG, RV, 8>(a, tiles, stream);
+    if constexpr (RV > 1) return launch_bwd_w<RK, KG, RV, 4>(a, tiles, stream);
+    return PALIMPSA_E_DIM;
 }
 
 static bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }

@@ -120,4 +120,50 @@ __device__ __forceinline__ long long seq_first_slot(const palimpsa_problem& p, i
     return (long long)n * ((p.seq_len + TB - 1) / TB);
 }
 
+// Store four values as duplicated pairs {x,x,y,y},{z,z,w,w} (operands of packed FP32 instructions).
+__device__ __forceinline__ void st_dup4(float4* dst, int i, float4 x) {
+    dst[2 * i] = make_float4(x.x, x.x, x.y, x.y);
+    dst[2 * i + 1] = make_float4(x.z, x.z, x.w, x.w);
+}
+
+
+// Sum N per-lane values over the L lanes that differ from this one in the low log2(L) bits
+// (L = 2^s <= 32).  "Transposed" butterfly: each step exchanges half of the remaining values, so it
+// costs N-1 (+ a few) shuffles instead of N*log2(L).  On return x[i], i < max(1, N/L), holds the sum of
+// value xreduce_index<N, L>(lane) + i.
+template <int N, int L>
+__device__ __forceinline__ void xreduce(float (&x)[N], int lane) {
+    int n = N;
+#pragma unroll
+    for (int off = L / 2; off >= 1; off >>= 1) {
+        if (n > 1) {
+            const int half = n / 2;
+            const bool up = (lane & off) != 0;
+#pragma unroll
+            for (int i = 0; i < N / 2; ++i) {
+                if (i < half) {
+                    const float keep = up ? x[i + half] : x[i];
+                    const float send = up ? x[i] : x[i + half];
+                    x[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                }
+            }
+            n = half;
+        } else {
+            x[0] += __shfl_xor_sync(0xffffffffu, x[0], off);
+        }
+    }
+}
+template <int N, int L>
+__device__ __forceinline__ int xreduce_index(int lane) {
+    int idx = 0, n = N;
+#pragma unroll
+    for (int off = L / 2; off >= 1; off >>= 1) {
+        if (n > 1) {
+            n /= 2;
+            if (lane & off) idx += n;
+        }
+    }
+    return idx;
+}
+
 }  // namespace palimpsa

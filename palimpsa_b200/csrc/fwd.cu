@@ -18,6 +18,8 @@
 // It serves the chunked op, the fused-recurrent op and the single-token decode step: what the
 // reference does with chunk_palimpsa_fwd_kernel (chunk_palimpsa_forgetting_scalar.py:66-218) and
 // fused_palimpsa_recurrent_fwd_kernel (fused_recurrent_palimpsa.py:24-154).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "host.h"
 
@@ -35,7 +37,7 @@ struct FwdArgs {
 };
 
 struct FwdSmem {
-    int qs, ks, kks, qqs, vs, bs, fc, ys, yvs;  // fp32 operand / result buffers (byte offsets)
+    int qs, ks, qqs, vs, bs, fc, ys, yvs;  // fp32 operand / result buffers (byte offsets)
     int raw;                                    // two raw stages follow each other from here
     int rq, rk, rv, rb, rgt, raw_stage;         // offsets inside a stage, stage size
     int total;
@@ -51,11 +53,10 @@ __host__ __device__ inline FwdSmem fwd_smem_layout(int KP, int TV, int es, bool 
     };
     s.qs = take(TB * KP * 4);
     s.ks = take(TB * KP * 4);
-    s.kks = take(TB * KP * 4);
     s.qqs = unc ? take(TB * KP * 4) : 0;
-    s.vs = take(TB * TV * 4);
-    s.bs = take(TB * TV * 4);
-    s.fc = take(TB * 8);
+    s.vs = take(TB * TV * 8);   // every value stored twice: {v, v}
+    s.bs = take(TB * TV * 8);
+    s.fc = take(TB * 16);       // {f, f, c, c}
     s.ys = take(TB * TV * 4);
     s.yvs = unc ? take(TB * TV * 4) : 0;
     s.raw = off;
@@ -114,7 +115,6 @@ __device__ __forceinline__ void fwd_convert(const FwdArgs& a, unsigned char* sm,
     const int K4 = KP / 4, V4 = TV / 4;
     float4* qs = reinterpret_cast<float4*>(sm + L.qs);
     float4* ks = reinterpret_cast<float4*>(sm + L.ks);
-    float4* kks = reinterpret_cast<float4*>(sm + L.kks);
     float4* qqs = reinterpret_cast<float4*>(sm + L.qqs);
     const float sc = p.scale;
     for (int i = tid; i < TB * K4; i += nthr) {
@@ -132,7 +132,6 @@ __device__ __forceinline__ void fwd_convert(const FwdArgs& a, unsigned char* sm,
         }
         qs[i] = make_float4(qv.x * sc, qv.y * sc, qv.z * sc, qv.w * sc);
         ks[i] = kv;
-        kks[i] = make_float4(kv.x * kv.x, kv.y * kv.y, kv.z * kv.z, kv.w * kv.w);
         if (UNC) qqs[i] = make_float4(sc * qv.x * qv.x, sc * qv.y * qv.y, sc * qv.z * qv.z, sc * qv.w * qv.w);
     }
     float4* vs = reinterpret_cast<float4*>(sm + L.vs);
@@ -150,25 +149,91 @@ __device__ __forceinline__ void fwd_convert(const FwdArgs& a, unsigned char* sm,
                 bv = ld4_guarded<DT>(p.b, row + v0 + c4 * 4, row + p.V);
             }
         }
-        vs[i] = vv;
-        bs[i] = bv;
+        st_dup4(vs, i, vv);
+        st_dup4(bs, i, bv);
     }
-    float2* fc = reinterpret_cast<float2*>(sm + L.fc);
+    float4* fc = reinterpret_cast<float4*>(sm + L.fc);
     for (int i = tid; i < TB; i += nthr) {
         float gtv = 0.f;
         if (i < nt) gtv = ALIGNED ? reinterpret_cast<const float*>(stage + L.rgt)[i] : p.gt[(tok0 + i) * p.H + h];
         float f = expf(-gtv * gh);
-        fc[i] = make_float2(f, (1.f - f) * iph);
+        const float c = (1.f - f) * iph;
+        fc[i] = make_float4(f, f, c, c);
     }
 }
 
-template <int RK, int KG, bool UNC>
-__global__ void __launch_bounds__(128) fwd_kernel(const FwdArgs a) {
-    constexpr int KP = RK * KG, VG = 32 / KG, RV = 2, J4 = RK / 4;
+// The recurrence over G consecutive tokens (no bounds checks: the caller only passes full groups),
+// followed by one batched reduction of the G*RV (x2 with uncertainty) output partials over the KG lanes
+// of the row group.  Kept free of conditionals on purpose: the state arrays M, I are updated in place.
+template <int RK, int KG, int RV, int TV, bool UNC, int G>
+__device__ __forceinline__ void fwd_group(float2 (&M)[RV][RK / 4][2], float2 (&I)[RV][RK / 4][2], const float4* ks4,
+                                          const float4* qs4, const float4* qqs4, const float2* vs2, const float2* bs2,
+                                          const float4* fc, float* ys, float* yvs, int tg, int kg, int row0, int lane) {
+    constexpr int KP = RK * KG, J4 = RK / 4, NRED = G * RV * (UNC ? 2 : 1);
+    float red[NRED];
+#pragma unroll
+    for (int jt = 0; jt < G; ++jt) {
+        const int t = tg + jt;
+        const float4 fcv = fc[t];
+        const float2 ff = make_float2(fcv.x, fcv.y), cc = make_float2(fcv.z, fcv.w);
+        float2 vr[RV], br[RV], acc[RV], accv[RV];
+#pragma unroll
+        for (int r = 0; r < RV; ++r) {
+            vr[r] = vs2[t * TV + r];
+            br[r] = bs2[t * TV + r];
+            acc[r] = accv[r] = make_float2(0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < J4; ++j) {
+            const int idx = t * (KP / 4) + j * KG + kg;
+            const float4 k4 = ks4[idx], q4 = qs4[idx];
+            float4 qq4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (UNC) qq4 = qqs4[idx];
+            const float2 kp[2] = {make_float2(k4.x, k4.y), make_float2(k4.z, k4.w)};
+            const float2 kkp[2] = {fmul2(kp[0], kp[0]), fmul2(kp[1], kp[1])};
+            const float2 qp[2] = {make_float2(q4.x, q4.y), make_float2(q4.z, q4.w)};
+            const float2 qqp[2] = {make_float2(qq4.x, qq4.y), make_float2(qq4.z, qq4.w)};
+#pragma unroll
+            for (int r = 0; r < RV; ++r) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    M[r][j][e] = ffma2(ff, M[r][j][e], fmul2(vr[r], kp[e]));
+                    I[r][j][e] = ffma2(ff, I[r][j][e], ffma2(br[r], kkp[e], cc));
+                    const float2 rr = rcp2(I[r][j][e]);
+                    acc[r] = ffma2(fmul2(M[r][j][e], rr), qp[e], acc[r]);
+                    if (UNC) accv[r] = ffma2(rr, qqp[e], accv[r]);
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < RV; ++r) {
+            red[(jt * RV + r) * (UNC ? 2 : 1)] = acc[r].x + acc[r].y;
+            if (UNC) red[(jt * RV + r) * 2 + 1] = accv[r].x + accv[r].y;
+        }
+    }
+    xreduce<NRED, KG>(red, lane);
+    constexpr int REM = NRED >= KG ? NRED / KG : 1;
+    const int base = xreduce_index<NRED, KG>(lane);
+    const bool owner = NRED >= KG ? true : (kg & (KG / (NRED < KG ? NRED : KG) - 1)) == 0;
+    if (owner) {
+#pragma unroll
+        for (int i = 0; i < REM; ++i) {
+            const int id = base + i;
+            const int which = UNC ? (id & 1) : 0;
+            const int jr = UNC ? (id >> 1) : id;
+            const int jt = jr / RV, r = jr % RV;
+            (which ? yvs : ys)[(tg + jt) * TV + row0 + r] = red[i];
+        }
+    }
+}
+
+template <int RK, int KG, int RV, int W, bool UNC>
+__global__ void __launch_bounds__(32 * W) fwd_kernel(const FwdArgs a) {
+    constexpr int KP = RK * KG, VG = 32 / KG, J4 = RK / 4, TV = W * VG * RV, NTHR = 32 * W;
+    constexpr int GF = 4;  // tokens whose outputs are reduced together
     extern __shared__ __align__(16) unsigned char sm[];
     const palimpsa_problem& p = a.p;
-    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, W = blockDim.x >> 5;
-    const int TV = W * VG * RV;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int kg = lane % KG, vg = lane / KG;
     const int row0 = (w * VG + vg) * RV;
     const int n = blockIdx.y / p.H, h = blockIdx.y - n * p.H;
@@ -224,11 +289,10 @@ __global__ void __launch_bounds__(128) fwd_kernel(const FwdArgs a) {
     const long long slot0 = seq_first_slot(p, n);
     const float4* qs4 = reinterpret_cast<const float4*>(sm + L.qs);
     const float4* ks4 = reinterpret_cast<const float4*>(sm + L.ks);
-    const float4* kks4 = reinterpret_cast<const float4*>(sm + L.kks);
     const float4* qqs4 = reinterpret_cast<const float4*>(sm + L.qqs);
-    const float* vs = reinterpret_cast<const float*>(sm + L.vs);
-    const float* bs = reinterpret_cast<const float*>(sm + L.bs);
-    const float2* fc = reinterpret_cast<const float2*>(sm + L.fc);
+    const float2* vs2 = reinterpret_cast<const float2*>(sm + L.vs) + row0;
+    const float2* bs2 = reinterpret_cast<const float2*>(sm + L.bs) + row0;
+    const float4* fc = reinterpret_cast<const float4*>(sm + L.fc);
     float* ys = reinterpret_cast<float*>(sm + L.ys);
     float* yvs = reinterpret_cast<float*>(sm + L.yvs);
     unsigned char* raw = sm + L.raw;
@@ -290,58 +354,18 @@ __global__ void __launch_bounds__(128) fwd_kernel(const FwdArgs a) {
             }
         }
 
-        // ---- the recurrence --------------------------------------------------------------------
-        for (int t = 0; t < nt; ++t) {
-            const float2 fcv = fc[t];
-            const float2 ff = dup2(fcv.x), cc = dup2(fcv.y);
-            const float2 vv = *reinterpret_cast<const float2*>(vs + t * TV + row0);
-            const float2 bv = *reinterpret_cast<const float2*>(bs + t * TV + row0);
-            const float2 vr[RV] = {dup2(vv.x), dup2(vv.y)};
-            const float2 br[RV] = {dup2(bv.x), dup2(bv.y)};
-            float2 acc[RV], accv[RV];
-#pragma unroll
-            for (int r = 0; r < RV; ++r) acc[r] = accv[r] = make_float2(0.f, 0.f);
-#pragma unroll
-            for (int j = 0; j < J4; ++j) {
-                const int idx = t * (KP / 4) + j * KG + kg;
-                const float4 k4 = ks4[idx], kk4 = kks4[idx], q4 = qs4[idx];
-                float4 qq4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (UNC) qq4 = qqs4[idx];
-                const float2 kp[2] = {make_float2(k4.x, k4.y), make_float2(k4.z, k4.w)};
-                const float2 kkp[2] = {make_float2(kk4.x, kk4.y), make_float2(kk4.z, kk4.w)};
-                const float2 qp[2] = {make_float2(q4.x, q4.y), make_float2(q4.z, q4.w)};
-                const float2 qqp[2] = {make_float2(qq4.x, qq4.y), make_float2(qq4.z, qq4.w)};
-#pragma unroll
-                for (int r = 0; r < RV; ++r) {
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        M[r][j][e] = ffma2(ff, M[r][j][e], fmul2(vr[r], kp[e]));
-                        I[r][j][e] = ffma2(ff, I[r][j][e], ffma2(br[r], kkp[e], cc));
-                        const float2 rr = rcp2(I[r][j][e]);
-                        acc[r] = ffma2(fmul2(M[r][j][e], rr), qp[e], acc[r]);
-                        if (UNC) accv[r] = ffma2(rr, qqp[e], accv[r]);
-                    }
-                }
-            }
-#pragma unroll
-            for (int r = 0; r < RV; ++r) {
-                float y = acc[r].x + acc[r].y;
-                float yv = accv[r].x + accv[r].y;
-#pragma unroll
-                for (int off = KG / 2; off >= 1; off >>= 1) {
-                    y += __shfl_xor_sync(0xffffffffu, y, off);
-                    if (UNC) yv += __shfl_xor_sync(0xffffffffu, yv, off);
-                }
-                if (kg == 0) {
-                    ys[t * TV + row0 + r] = y;
-                    if (UNC) yvs[t * TV + row0 + r] = yv;
-                }
-            }
-        }
+        // ---- the recurrence: full groups of GF tokens, then the remaining tokens one by one --------
+        int tg = 0;
+#pragma unroll 1
+        for (; tg + GF <= nt; tg += GF)
+            fwd_group<RK, KG, RV, TV, UNC, GF>(M, I, ks4, qs4, qqs4, vs2, bs2, fc, ys, yvs, tg, kg, row0, lane);
+#pragma unroll 1
+        for (; tg < nt; ++tg)
+            fwd_group<RK, KG, RV, TV, UNC, 1>(M, I, ks4, qs4, qqs4, vs2, bs2, fc, ys, yvs, tg, kg, row0, lane);
         __syncthreads();
 
         // ---- write the block's outputs -----------------------------------------------------------
-        for (int i = tid; i < nt * TV; i += blockDim.x) {
+        for (int i = tid; i < nt * TV; i += NTHR) {
             const int t = i / TV, r = i - t * TV;
             if (r < tvw) {
                 const long long e = ((tok0 + t) * p.H + h) * (long long)V + v0 + r;
@@ -386,31 +410,36 @@ __global__ void __launch_bounds__(128) fwd_kernel(const FwdArgs a) {
 // -------------------------------------------------------------------------------------------------
 // Host side
 // -------------------------------------------------------------------------------------------------
-template <int RK, int KG>
-static int launch_fwd_t(const FwdArgs& a, cudaStream_t stream) {
-    constexpr int VG = 32 / KG, RPW = VG * 2;  // state rows per warp
+template <int RK, int KG, int RV, int W>
+static int launch_fwd_w(const FwdArgs& a, cudaStream_t stream) {
+    constexpr int VG = 32 / KG, TV = W * VG * RV;
     const palimpsa_problem& p = a.p;
-    int W = 4;
-    if (p.V <= RPW && RPW >= 8)
-        W = 1;
-    else if (p.V <= 2 * RPW)
-        W = 2;
-    const int TV = W * RPW;
     const bool unc = (p.flags & PALIMPSA_FLAG_UNCERTAINTY) != 0;
     const FwdSmem L = fwd_smem_layout(RK * KG, TV, dtype_size(p.io_dtype), unc);
     dim3 grid((p.V + TV - 1) / TV, p.num_seqs * p.H, 1);
     dim3 block(32 * W, 1, 1);
     cudaError_t e;
     if (unc) {
-        e = cudaFuncSetAttribute(fwd_kernel<RK, KG, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+        e = cudaFuncSetAttribute(fwd_kernel<RK, KG, RV, W, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
         if (e != cudaSuccess) return PALIMPSA_E_LAUNCH;
-        fwd_kernel<RK, KG, true><<<grid, block, L.total, stream>>>(a);
+        fwd_kernel<RK, KG, RV, W, true><<<grid, block, L.total, stream>>>(a);
     } else {
-        e = cudaFuncSetAttribute(fwd_kernel<RK, KG, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+        e = cudaFuncSetAttribute(fwd_kernel<RK, KG, RV, W, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
         if (e != cudaSuccess) return PALIMPSA_E_LAUNCH;
-        fwd_kernel<RK, KG, false><<<grid, block, L.total, stream>>>(a);
+        fwd_kernel<RK, KG, RV, W, false><<<grid, block, L.total, stream>>>(a);
     }
     return cudaGetLastError() == cudaSuccess ? PALIMPSA_OK : PALIMPSA_E_LAUNCH;
+}
+
+// Warps per CTA: WMAX, or fewer when d_v is short (the row tile stays a multiple of 8 rows).
+template <int RK, int KG, int RV, int WMAX>
+static int launch_fwd_t(const FwdArgs& a, cudaStream_t stream) {
+    constexpr int RPW = (32 / KG) * RV;
+    if constexpr (WMAX >= 4 && (RPW * (WMAX / 4)) % 8 == 0)
+        if (a.p.V <= RPW * (WMAX / 4)) return launch_fwd_w<RK, KG, RV, WMAX / 4>(a, stream);
+    if constexpr (WMAX >= 2 && (RPW * (WMAX / 2)) % 8 == 0)
+        if (a.p.V <= RPW * (WMAX / 2)) return launch_fwd_w<RK, KG, RV, WMAX / 2>(a, stream);
+    return launch_fwd_w<RK, KG, RV, WMAX>(a, stream);
 }
 
 static bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
@@ -428,15 +457,25 @@ int launch_fwd(const palimpsa_fwd_params* prm, cudaStream_t stream) {
     const int es = dtype_size(p.io_dtype);
     a.aligned = ((p.K * es) % 16 == 0) && ((p.V * es) % 16 == 0) && aligned16(p.q) && aligned16(p.k) &&
                 aligned16(p.v) && aligned16(p.b) && ((reinterpret_cast<uintptr_t>(p.gt) & 3) == 0);
+    // development knob: PALIMPSA_FWD_CFG=<n> selects an alternative thread tiling for d_k = 128
+    static const int cfg = [] {
+        const char* e = getenv("PALIMPSA_FWD_CFG");
+        return e ? atoi(e) : 0;
+    }();
     switch (palimpsa_padded_k(p.K)) {
-        case 16: return launch_fwd_t<8, 2>(a, stream);
-        case 32: return launch_fwd_t<8, 4>(a, stream);
-        case 48: return launch_fwd_t<12, 4>(a, stream);
-        case 64: return launch_fwd_t<16, 4>(a, stream);
-        case 96: return launch_fwd_t<12, 8>(a, stream);
-        case 128: return launch_fwd_t<16, 8>(a, stream);
-        case 192: return launch_fwd_t<12, 16>(a, stream);
-        case 256: return launch_fwd_t<16, 16>(a, stream);
+        case 16: return launch_fwd_t<8, 2, 2, 2>(a, stream);
+        case 32: return launch_fwd_t<8, 4, 2, 4>(a, stream);
+        case 48: return launch_fwd_t<12, 4, 2, 4>(a, stream);
+        case 64: return launch_fwd_t<16, 4, 2, 2>(a, stream);
+        case 96: return launch_fwd_t<12, 8, 2, 4>(a, stream);
+        case 128:
+            if (cfg == 1) return launch_fwd_t<8, 16, 2, 4>(a, stream);
+            if (cfg == 2) return launch_fwd_t<4, 32, 2, 4>(a, stream);
+            if (cfg == 3) return launch_fwd_t<4, 32, 4, 4>(a, stream);
+            if (cfg == 4) return launch_fwd_t<8, 16, 4, 4>(a, stream);
+            return launch_fwd_t<16, 8, 2, 4>(a, stream);
+        case 192: return launch_fwd_t<12, 16, 2, 4>(a, stream);
+        case 256: return launch_fwd_t<16, 16, 2, 4>(a, stream);
         default: return PALIMPSA_E_DIM;
     }
 }
