@@ -1,8 +1,8 @@
 """palimpsa_b200: the Palimpsa operator (Bayesian-metaplastic linear attention) as hand-written
 sm_100a CUDA behind the reference's ``palimpsa.ops`` Python interface."""
-from .ops import chunk_palimpsa, fused_recurrent_palimpsa, palimpsa_ref
+from .ops import chunk_palimpsa, decode_step, fused_recurrent_palimpsa, palimpsa_ref
 
-__all__ = ["chunk_palimpsa", "fused_recurrent_palimpsa", "palimpsa_ref", "install_as_palimpsa_ops"]
+__all__ = ["chunk_palimpsa", "fused_recurrent_palimpsa", "palimpsa_ref", "decode_step", "install_as_palimpsa_ops"]
 
 
 def install_as_palimpsa_ops():

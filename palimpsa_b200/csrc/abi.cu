@@ -105,6 +105,7 @@ int palimpsa_chunk_fwd(const palimpsa_fwd_params* prm, void* cuda_stream) {
 int palimpsa_recurrent_fwd(const palimpsa_fwd_params* prm, void* cuda_stream) {
     int rc = check_fwd(prm);
     if (rc) return rc;
+    if (decode_supported(prm)) return launch_decode(prm, static_cast<cudaStream_t>(cuda_stream));
     return launch_fwd(prm, static_cast<cudaStream_t>(cuda_stream));
 }
 
@@ -115,6 +116,7 @@ int palimpsa_decode_step(const palimpsa_fwd_params* prm, void* cuda_stream) {
     if (p.cu_seqlens || p.seq_len != 1 || p.total_tokens != p.num_seqs) return PALIMPSA_E_SHAPE;
     if (!p.init_mu || !prm->final_mu) return PALIMPSA_E_NULL;
     if (prm->ckpt_M) return PALIMPSA_E_SHAPE;
+    if (decode_supported(prm)) return launch_decode(prm, static_cast<cudaStream_t>(cuda_stream));
     return launch_fwd(prm, static_cast<cudaStream_t>(cuda_stream));
 }
 

@@ -469,11 +469,11 @@ int launch_fwd(const palimpsa_fwd_params* prm, cudaStream_t stream) {
         case 64: return launch_fwd_t<16, 4, 2, 2>(a, stream);
         case 96: return launch_fwd_t<12, 8, 2, 4>(a, stream);
         case 128:
-            if (cfg == 1) return launch_fwd_t<8, 16, 2, 4>(a, stream);
+            if (cfg == 1) return launch_fwd_t<16, 8, 2, 4>(a, stream);
             if (cfg == 2) return launch_fwd_t<4, 32, 2, 4>(a, stream);
             if (cfg == 3) return launch_fwd_t<4, 32, 4, 4>(a, stream);
             if (cfg == 4) return launch_fwd_t<8, 16, 4, 4>(a, stream);
-            return launch_fwd_t<16, 8, 2, 4>(a, stream);
+            return launch_fwd_t<8, 16, 2, 4>(a, stream);
         case 192: return launch_fwd_t<12, 16, 2, 4>(a, stream);
         case 256: return launch_fwd_t<16, 16, 2, 4>(a, stream);
         default: return PALIMPSA_E_DIM;

@@ -10,6 +10,10 @@ namespace palimpsa {
 // Enqueue the forward kernel (fwd.cu).  Parameters are assumed validated.
 int launch_fwd(const palimpsa_fwd_params* prm, cudaStream_t stream);
 
+// Single-token decode step (decode.cu): dedicated HBM-bound kernel, when it covers the call.
+bool decode_supported(const palimpsa_fwd_params* prm);
+int launch_decode(const palimpsa_fwd_params* prm, cudaStream_t stream);
+
 // Backward (bwd.cu): main kernel (stages bit 0) + the two finishing kernels (bit 1).
 int launch_bwd(const palimpsa_bwd_params* prm, cudaStream_t stream, int stages);
 
