@@ -213,8 +213,8 @@ def kernel_roofline(d, cfg, steps, peaks):
     B, T, H, K, V = cfg["B"], cfg["T"], cfg["H"], cfg["K"], cfg["V"]
     q, k, v, b, gt, g, Ip, do = [d[n] for n in ("q", "k", "v", "b", "gt", "g", "Ip", "do")]
     with torch.no_grad():
-        _, _, _, _, ckM, ckI, _ = _core.fwd_op(q, k, v, b, gt, g, Ip, None, None, None, K ** -0.5, False, True, False,
-                                               False)
+        _, _, _, _, ckM, ckI, _, _ = _core.fwd_op(q, k, v, b, gt, g, Ip, None, None, None, K ** -0.5, False, True, False,
+                                                  False, 1)
     dq, dk, dv, db = [torch.empty_like(x) for x in (q, k, v, b)]
     dgt = torch.empty(B, T, H, device=q.device)
     dg, dIp = torch.empty(H, device=q.device), torch.empty(H, device=q.device)

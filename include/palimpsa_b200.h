@@ -37,7 +37,7 @@
 extern "C" {
 #endif
 
-#define PALIMPSA_ABI_VERSION 3
+#define PALIMPSA_ABI_VERSION 4
 
 /* io dtype of q, k, v, b, o, o_var, do, do_var, dq, dk, dv, db */
 #define PALIMPSA_F32 0
@@ -112,6 +112,53 @@ typedef struct palimpsa_bwd_params {
     void *workspace;       /* scratch, >= palimpsa_bwd_workspace_bytes(), 256-byte aligned       */
     size_t workspace_bytes;
 } palimpsa_bwd_params;
+
+/* Segments.  A sequence may be cut into G segments of seg_len tokens (a multiple of 16) that are
+ * processed by different CTAs -- or by different GPUs (context parallelism), where each rank's
+ * share of the sequence is its own problem and the boundary states travel between ranks.  The
+ * recurrence is linear in (M, J = I - Ip) with a scalar decay per head, so segment g's start state
+ * follows from the zero-start summaries of the segments before it:
+ *     S_{g+1} = decay_g * S_g + sum_g.
+ * The reference has no counterpart: it walks every sequence serially in one program
+ * (chunk_palimpsa_forgetting_scalar.py:128-142) and has no context parallelism.
+ * All buffers are float32, [N, G, H, V, KP] unless noted; those a call does not use may be NULL. */
+typedef struct palimpsa_segments {
+    int32_t num_segments;      /* G >= 1                                                        */
+    int32_t seg_len;           /* tokens per segment, multiple of 16; G*seg_len >= longest seq   */
+    float *sum_M, *sum_J;      /* end state of each segment when started from zero, (M, J) form  */
+    float *decay;              /* [N, G, H] product of f over the segment                        */
+    float *start_M, *start_I;  /* state at the start of each segment, (M, I) form                */
+    float *carry_M, *carry_I;  /* backward: dL/d(end state of the segment), (M, I) form          */
+    float *rloc_M, *rloc_I;    /* backward: dL/d(start state of the segment), (M, I) form        */
+} palimpsa_segments;
+
+/* Fills sum_M, sum_J and decay for every segment (no reciprocal, no output: the cheap pass). */
+int palimpsa_segment_summary(const palimpsa_problem *p, const palimpsa_segments *segs, void *cuda_stream);
+
+/* Forward boundary scan: start_M/start_I of every segment from the summaries.  The state before
+ * segment 0 is (in_M, in_J) [N,H,V,KP] in (M, J) form if given (a previous rank's end state), else
+ * p->init_mu/init_I, else the prior (0, 0).  If out_M/out_J are given they receive the state after
+ * the last segment, (M, J) form: what the next rank needs. */
+int palimpsa_cp_combine(const palimpsa_problem *p, const palimpsa_segments *segs, const float *in_M,
+                        const float *in_J, float *out_M, float *out_J, void *cuda_stream);
+
+/* Backward boundary scan: carry_M/carry_I of every segment from the zero-carry start-state
+ * gradients in rloc_M/rloc_I and decay:  carry_{g-1} = rloc_g + decay_g * carry_g.  (in_M, in_I)
+ * [N,H,V,KP] is dL/d(end state of the last segment) (a later rank's out), or NULL for zero;
+ * (out_M, out_I), if given, receive dL/d(start state of segment 0). */
+int palimpsa_cp_combine_bwd(const palimpsa_problem *p, const palimpsa_segments *segs, const float *in_M,
+                            const float *in_I, float *out_M, float *out_I, void *cuda_stream);
+
+/* palimpsa_chunk_fwd with every segment started from segs->start_M/start_I. */
+int palimpsa_chunk_fwd_segments(const palimpsa_fwd_params *params, const palimpsa_segments *segs,
+                                void *cuda_stream);
+
+/* palimpsa_chunk_bwd per segment.  carry_only != 0: only propagate the state gradients from a zero
+ * end-state gradient and write rloc_M/rloc_I (no other output is touched, no workspace needed).
+ * carry_only == 0: full backward with segs->carry_M/carry_I (NULL = zero) as end-state gradients;
+ * rloc_M/rloc_I, if given, receive the start-state gradients. */
+int palimpsa_chunk_bwd_segments(const palimpsa_bwd_params *params, const palimpsa_segments *segs,
+                                int carry_only, void *cuda_stream);
 
 /* Version of this header the library was built from. */
 int palimpsa_abi_version(void);

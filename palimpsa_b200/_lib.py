@@ -7,7 +7,7 @@ import os
 PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libpalimpsa_b200.so")
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 F32, BF16, F16 = 0, 1, 2
 FLAG_UNCERTAINTY = 1
 FLAG_EXPLICIT_INIT = 2
@@ -48,12 +48,29 @@ class BwdParams(C.Structure):
     ]
 
 
+class Segments(C.Structure):
+    _fields_ = [
+        ("num_segments", C.c_int32), ("seg_len", C.c_int32),
+        ("sum_M", C.c_void_p), ("sum_J", C.c_void_p), ("decay", C.c_void_p),
+        ("start_M", C.c_void_p), ("start_I", C.c_void_p),
+        ("carry_M", C.c_void_p), ("carry_I", C.c_void_p),
+        ("rloc_M", C.c_void_p), ("rloc_I", C.c_void_p),
+    ]
+
+
 # every symbol include/palimpsa_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "palimpsa_abi_version": (C.c_int, []),
     "palimpsa_last_error_string": (C.c_char_p, [C.c_int]),
     "palimpsa_padded_k": (C.c_int, [C.c_int]),
     "palimpsa_ckpt_slots": (C.c_longlong, [C.POINTER(Problem)]),
+    "palimpsa_segment_summary": (C.c_int, [C.POINTER(Problem), C.POINTER(Segments), C.c_void_p]),
+    "palimpsa_cp_combine": (C.c_int, [C.POINTER(Problem), C.POINTER(Segments), C.c_void_p, C.c_void_p, C.c_void_p,
+                                      C.c_void_p, C.c_void_p]),
+    "palimpsa_cp_combine_bwd": (C.c_int, [C.POINTER(Problem), C.POINTER(Segments), C.c_void_p, C.c_void_p, C.c_void_p,
+                                          C.c_void_p, C.c_void_p]),
+    "palimpsa_chunk_fwd_segments": (C.c_int, [C.POINTER(FwdParams), C.POINTER(Segments), C.c_void_p]),
+    "palimpsa_chunk_bwd_segments": (C.c_int, [C.POINTER(BwdParams), C.POINTER(Segments), C.c_int, C.c_void_p]),
     "palimpsa_chunk_fwd": (C.c_int, [C.POINTER(FwdParams), C.c_void_p]),
     "palimpsa_recurrent_fwd": (C.c_int, [C.POINTER(FwdParams), C.c_void_p]),
     "palimpsa_decode_step": (C.c_int, [C.POINTER(FwdParams), C.c_void_p]),

@@ -40,16 +40,16 @@ int check_fwd(const palimpsa_fwd_params* prm) {
     return PALIMPSA_OK;
 }
 
-int check_bwd(const palimpsa_bwd_params* prm, bool caller_workspace = true) {
+int check_bwd(const palimpsa_bwd_params* prm, bool caller_workspace = true, bool need_outputs = true) {
     if (!prm) return PALIMPSA_E_NULL;
     if (prm->struct_size != sizeof(palimpsa_bwd_params)) return PALIMPSA_E_VERSION;
     int rc = check_problem(prm->p);
     if (rc) return rc;
     const palimpsa_problem& p = prm->p;
-    if (!prm->dg || !prm->dIp) return PALIMPSA_E_NULL;
+    if (need_outputs && (!prm->dg || !prm->dIp)) return PALIMPSA_E_NULL;
     if (p.total_tokens > 0) {
-        if (!prm->d_o || !prm->ckpt_M || !prm->ckpt_I || !prm->dq || !prm->dk || !prm->dv || !prm->db || !prm->dgt)
-            return PALIMPSA_E_NULL;
+        if (!prm->d_o || !prm->ckpt_M || !prm->ckpt_I) return PALIMPSA_E_NULL;
+        if (need_outputs && (!prm->dq || !prm->dk || !prm->dv || !prm->db || !prm->dgt)) return PALIMPSA_E_NULL;
         if ((p.flags & PALIMPSA_FLAG_UNCERTAINTY) && !prm->d_o_var) return PALIMPSA_E_NULL;
     }
     if (misaligned16(prm->ckpt_M) || misaligned16(prm->ckpt_I)) return PALIMPSA_E_ALIGN;
@@ -58,6 +58,17 @@ int check_bwd(const palimpsa_bwd_params* prm, bool caller_workspace = true) {
     if (!caller_workspace) return PALIMPSA_OK;
     if (!prm->workspace || prm->workspace_bytes < need) return PALIMPSA_E_WORKSPACE;
     if (reinterpret_cast<uintptr_t>(prm->workspace) & 255) return PALIMPSA_E_WORKSPACE;
+    return PALIMPSA_OK;
+}
+
+int check_segments(const palimpsa_problem& p, const palimpsa_segments* sg) {
+    if (!sg) return PALIMPSA_E_NULL;
+    if (sg->num_segments < 1 || sg->seg_len <= 0 || sg->seg_len % PALIMPSA_CKPT_INTERVAL) return PALIMPSA_E_SHAPE;
+    if (!p.cu_seqlens && (long long)sg->num_segments * sg->seg_len < p.seq_len) return PALIMPSA_E_SHAPE;
+    if (palimpsa_padded_k(p.K) == 0) return PALIMPSA_E_DIM;
+    const void* ptrs[] = {sg->sum_M, sg->sum_J, sg->start_M, sg->start_I, sg->carry_M, sg->carry_I, sg->rloc_M, sg->rloc_I};
+    for (const void* x : ptrs)
+        if (misaligned16(x)) return PALIMPSA_E_ALIGN;
     return PALIMPSA_OK;
 }
 
@@ -99,14 +110,14 @@ long long palimpsa_ckpt_slots(const palimpsa_problem* p) {
 int palimpsa_chunk_fwd(const palimpsa_fwd_params* prm, void* cuda_stream) {
     int rc = check_fwd(prm);
     if (rc) return rc;
-    return launch_fwd(prm, static_cast<cudaStream_t>(cuda_stream));
+    return launch_fwd(prm, nullptr, false, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int palimpsa_recurrent_fwd(const palimpsa_fwd_params* prm, void* cuda_stream) {
     int rc = check_fwd(prm);
     if (rc) return rc;
     if (decode_supported(prm)) return launch_decode(prm, static_cast<cudaStream_t>(cuda_stream));
-    return launch_fwd(prm, static_cast<cudaStream_t>(cuda_stream));
+    return launch_fwd(prm, nullptr, false, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int palimpsa_decode_step(const palimpsa_fwd_params* prm, void* cuda_stream) {
@@ -117,7 +128,67 @@ int palimpsa_decode_step(const palimpsa_fwd_params* prm, void* cuda_stream) {
     if (!p.init_mu || !prm->final_mu) return PALIMPSA_E_NULL;
     if (prm->ckpt_M) return PALIMPSA_E_SHAPE;
     if (decode_supported(prm)) return launch_decode(prm, static_cast<cudaStream_t>(cuda_stream));
-    return launch_fwd(prm, static_cast<cudaStream_t>(cuda_stream));
+    return launch_fwd(prm, nullptr, false, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int palimpsa_segment_summary(const palimpsa_problem* p, const palimpsa_segments* sg, void* cuda_stream) {
+    if (!p) return PALIMPSA_E_NULL;
+    int rc = check_problem(*p);
+    if (rc) return rc;
+    rc = check_segments(*p, sg);
+    if (rc) return rc;
+    if (!sg->sum_M || !sg->sum_J || !sg->decay) return PALIMPSA_E_NULL;
+    palimpsa_fwd_params prm{};
+    prm.struct_size = sizeof(prm);
+    prm.p = *p;
+    return launch_fwd(&prm, sg, true, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int palimpsa_cp_combine(const palimpsa_problem* p, const palimpsa_segments* sg, const float* in_M, const float* in_J,
+                        float* out_M, float* out_J, void* cuda_stream) {
+    if (!p) return PALIMPSA_E_NULL;
+    int rc = check_problem(*p);
+    if (rc) return rc;
+    rc = check_segments(*p, sg);
+    if (rc) return rc;
+    if (!sg->sum_M || !sg->sum_J || !sg->decay || !sg->start_M || !sg->start_I) return PALIMPSA_E_NULL;
+    if ((in_M == nullptr) != (in_J == nullptr) || (out_M == nullptr) != (out_J == nullptr)) return PALIMPSA_E_NULL;
+    if (misaligned16(in_M) || misaligned16(in_J) || misaligned16(out_M) || misaligned16(out_J)) return PALIMPSA_E_ALIGN;
+    return launch_combine_fwd(*p, *sg, in_M, in_J, out_M, out_J, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int palimpsa_cp_combine_bwd(const palimpsa_problem* p, const palimpsa_segments* sg, const float* in_M,
+                            const float* in_I, float* out_M, float* out_I, void* cuda_stream) {
+    if (!p) return PALIMPSA_E_NULL;
+    int rc = check_problem(*p);
+    if (rc) return rc;
+    rc = check_segments(*p, sg);
+    if (rc) return rc;
+    if (!sg->decay || !sg->carry_M || !sg->carry_I || !sg->rloc_M || !sg->rloc_I) return PALIMPSA_E_NULL;
+    if ((in_M == nullptr) != (in_I == nullptr) || (out_M == nullptr) != (out_I == nullptr)) return PALIMPSA_E_NULL;
+    if (misaligned16(in_M) || misaligned16(in_I) || misaligned16(out_M) || misaligned16(out_I)) return PALIMPSA_E_ALIGN;
+    return launch_combine_bwd(*p, *sg, in_M, in_I, out_M, out_I, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int palimpsa_chunk_fwd_segments(const palimpsa_fwd_params* prm, const palimpsa_segments* sg, void* cuda_stream) {
+    int rc = check_fwd(prm);
+    if (rc) return rc;
+    rc = check_segments(prm->p, sg);
+    if (rc) return rc;
+    if (!sg->start_M || !sg->start_I) return PALIMPSA_E_NULL;
+    return launch_fwd(prm, sg, false, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int palimpsa_chunk_bwd_segments(const palimpsa_bwd_params* prm, const palimpsa_segments* sg, int carry_only,
+                                void* cuda_stream) {
+    int rc = check_bwd(prm, carry_only == 0, carry_only == 0);
+    if (rc) return rc;
+    rc = check_segments(prm->p, sg);
+    if (rc) return rc;
+    if ((sg->carry_M == nullptr) != (sg->carry_I == nullptr) || (sg->rloc_M == nullptr) != (sg->rloc_I == nullptr))
+        return PALIMPSA_E_NULL;
+    if (carry_only && !sg->rloc_M) return PALIMPSA_E_NULL;
+    return launch_bwd(prm, sg, carry_only != 0, static_cast<cudaStream_t>(cuda_stream), 3);
 }
 
 size_t palimpsa_bwd_workspace_bytes(const palimpsa_problem* p) {
@@ -128,14 +199,14 @@ size_t palimpsa_bwd_workspace_bytes(const palimpsa_problem* p) {
 int palimpsa_chunk_bwd(const palimpsa_bwd_params* prm, void* cuda_stream) {
     int rc = check_bwd(prm);
     if (rc) return rc;
-    return launch_bwd(prm, static_cast<cudaStream_t>(cuda_stream), 3);
+    return launch_bwd(prm, nullptr, false, static_cast<cudaStream_t>(cuda_stream), 3);
 }
 
 int palimpsa_chunk_bwd_stages(const palimpsa_bwd_params* prm, void* cuda_stream, int stages) {
     int rc = check_bwd(prm);
     if (rc) return rc;
     if (stages < 1 || stages > 3) return PALIMPSA_E_SHAPE;
-    return launch_bwd(prm, static_cast<cudaStream_t>(cuda_stream), stages);
+    return launch_bwd(prm, nullptr, false, static_cast<cudaStream_t>(cuda_stream), stages);
 }
 
 int palimpsa_chunk_bwd_static(const palimpsa_bwd_params* prm, void* cuda_stream) {
@@ -147,7 +218,7 @@ int palimpsa_chunk_bwd_static(const palimpsa_bwd_params* prm, void* cuda_stream)
 int palimpsa_recurrent_bwd(const palimpsa_bwd_params* prm, void* cuda_stream) {
     int rc = check_bwd(prm);
     if (rc) return rc;
-    return launch_bwd(prm, static_cast<cudaStream_t>(cuda_stream), 3);
+    return launch_bwd(prm, nullptr, false, static_cast<cudaStream_t>(cuda_stream), 3);
 }
 
 }  // extern "C"

@@ -40,6 +40,12 @@ struct BwdArgs {
     void *dv, *db;
     int aligned;
     int rows_total;  // tokens * H
+    // segments (gridDim.z of them per sequence; seg_len tokens each, a multiple of 16; 0 = whole sequence)
+    int seg_len;
+    const float* carry_M;  // [N,G,H,V,KP] dL/d(end state of the segment), (M, I) form, or NULL (zero)
+    const float* carry_I;
+    float* rloc_M;         // [N,G,H,V,KP] dL/d(start state of the segment), or NULL
+    float* rloc_I;
 };
 
 struct BwdSmem {
@@ -143,7 +149,8 @@ __device__ __forceinline__ void bwd_issue_raw(const BwdArgs& a, unsigned char* s
 
 template <int DT, bool ALIGNED, bool UNC>
 __device__ __forceinline__ void bwd_convert(const BwdArgs& a, unsigned char* sm, const BwdSmem& L, int KP, int TV,
-                                            long long tok0, int nt, int nt_ext, int h, int v0, float gh, float iph) {
+                                            long long tok0, int nt, int nt_ext, int h, int v0, float gh, float iph,
+                                            bool carry_block) {
     const palimpsa_problem& p = a.p;
     const int nthr = blockDim.x, tid = threadIdx.x;
     const int K4 = KP / 4, V4 = TV / 4;
@@ -210,7 +217,10 @@ __device__ __forceinline__ void bwd_convert(const BwdArgs& a, unsigned char* sm,
             if (has1) g1 = p.gt[(tok0 + i + 1) * p.H + h];
         }
         const float f = expf(-g0 * gh);
-        const float fn = has1 ? expf(-g1 * gh) : 0.f;
+        float fn = has1 ? expf(-g1 * gh) : 0.f;
+        // Last block of a segment whose end-state gradient is supplied: that gradient is already expressed
+        // at the boundary, so the last real token (and any identity padding after it) passes it on undecayed.
+        if (carry_block && i >= nt - 1) fn = 1.f;
         const float c = (1.f - f) * iph;
         fc2[i] = make_float4(f, f, c, c);
         fn2[i] = make_float2(fn, fn);
@@ -222,7 +232,7 @@ struct State {
     float2 M[RV][NP], I[RV][NP];
 };
 
-template <int RK, int KG, int RV, int W, bool UNC>
+template <int RK, int KG, int RV, int W, bool UNC, bool CO>
 __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
     constexpr int KP = RK * KG, VG = 32 / KG, NP = RK / 2, NE = RV * RK, KP2 = KP / 2;
     constexpr int TV = W * VG * RV, WV = W * VG, NTHR = 32 * W;
@@ -242,11 +252,32 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
     const BwdSmem L = bwd_smem_layout(KP, TV, NE, NTHR, WV, es, UNC);
     int bos, len;
     seq_range(p, n, bos, len);
-    if (len <= 0) return;
+    // this CTA's segment of the sequence: tokens [s0, s1), blocks [blk0, blk1)
+    const int g = blockIdx.z, G = gridDim.z;
+    const int s0 = a.seg_len > 0 ? min(len, g * a.seg_len) : 0;
+    const int s1 = a.seg_len > 0 ? min(len, s0 + a.seg_len) : len;
+    const long long seg_base = (((long long)n * G + g) * p.H + h) * p.V;  // row index into [N,G,H,V,KP] buffers
+    if (s1 <= s0) {  // empty segment: the end-state gradient is the start-state gradient
+        if (a.rloc_M) {
+            for (int i = tid; i < tvw * (KP / 4); i += NTHR) {
+                const long long e = (seg_base + v0) * KP + (long long)i * 4;
+                float4 cm = make_float4(0.f, 0.f, 0.f, 0.f), ci = cm;
+                if (!CO && a.carry_M) {
+                    cm = *reinterpret_cast<const float4*>(a.carry_M + e);
+                    ci = *reinterpret_cast<const float4*>(a.carry_I + e);
+                }
+                *reinterpret_cast<float4*>(a.rloc_M + e) = cm;
+                *reinterpret_cast<float4*>(a.rloc_I + e) = ci;
+            }
+        }
+        return;
+    }
     const float gh = p.g[h], iph = p.Ip[h];
     const int V = p.V;
     const long long slot0 = seq_first_slot(p, n);
-    const int nblk = (len + TB - 1) / TB;
+    const int blk0 = s0 / TB, blk1 = (s1 + TB - 1) / TB;
+    const int nblk = blk1 - blk0;
+    const bool has_carry = !CO && a.carry_M != nullptr;
     const bool has_init = p.init_mu != nullptr || (p.flags & PALIMPSA_FLAG_EXPLICIT_INIT);
 
     // this thread's d_k columns are RK*kg .. RK*kg+RK-1: pair q covers columns RK*kg + 2q, +1
@@ -270,7 +301,16 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
 #pragma unroll
     for (int r = 0; r < RV; ++r)
 #pragma unroll
-        for (int q = 0; q < NP; ++q) GM[r][q] = nGI[r][q] = make_float2(0.f, 0.f);
+        for (int q = 0; q < NP; ++q) {
+            GM[r][q] = nGI[r][q] = make_float2(0.f, 0.f);
+            if (has_carry && row0 + r < tvw) {
+                const long long e = (seg_base + v0 + row0 + r) * KP + RK * kg + 2 * q;
+                const float2 cm = *reinterpret_cast<const float2*>(a.carry_M + e);
+                const float2 ci = *reinterpret_cast<const float2*>(a.carry_I + e);
+                GM[r][q] = cm;
+                nGI[r][q] = make_float2(-ci.x, -ci.y);
+            }
+        }
 
     auto load_ck = [&](State<RV, NP>& s, int stage_idx) {
         const float* ckM = reinterpret_cast<const float*>(sm + L.ckb + stage_idx * L.ck_stage);
@@ -328,7 +368,7 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
     };
 
     {
-        const int c = nblk - 1;
+        const int c = blk1 - 1;
         const int nt = min(TB, len - c * TB);
         bwd_issue_ckpt(a, sm, L, 0, KP, TV, slot0 + c, h, v0, tvw);
         if (a.aligned) bwd_issue_raw(a, sm, L, es, KP, TV, (long long)bos + c * TB, nt, nt, h, v0, tvw);
@@ -336,7 +376,8 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
     }
 
     for (int it = 0; it < nblk; ++it) {
-        const int c = nblk - 1 - it;
+        const int c = blk1 - 1 - it;
+        const bool cblk = has_carry && it == 0;
         const int t0 = c * TB;
         const int nt = min(TB, len - t0);
         const int nt_ext = min(TB + 1, len - t0);
@@ -346,22 +387,22 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
         __syncthreads();
         if (a.aligned) {
             if (p.io_dtype == PALIMPSA_BF16)
-                bwd_convert<PALIMPSA_BF16, true, UNC>(a, sm, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
+                bwd_convert<PALIMPSA_BF16, true, UNC>(a, sm, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph, cblk);
             else if (p.io_dtype == PALIMPSA_F32)
-                bwd_convert<PALIMPSA_F32, true, UNC>(a, sm, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
+                bwd_convert<PALIMPSA_F32, true, UNC>(a, sm, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph, cblk);
             else
-                bwd_convert<PALIMPSA_F16, true, UNC>(a, sm, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
+                bwd_convert<PALIMPSA_F16, true, UNC>(a, sm, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph, cblk);
         } else {
             if (p.io_dtype == PALIMPSA_BF16)
-                bwd_convert<PALIMPSA_BF16, false, UNC>(a, sm, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
+                bwd_convert<PALIMPSA_BF16, false, UNC>(a, sm, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph, cblk);
             else if (p.io_dtype == PALIMPSA_F32)
-                bwd_convert<PALIMPSA_F32, false, UNC>(a, sm, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
+                bwd_convert<PALIMPSA_F32, false, UNC>(a, sm, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph, cblk);
             else
-                bwd_convert<PALIMPSA_F16, false, UNC>(a, sm, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph);
+                bwd_convert<PALIMPSA_F16, false, UNC>(a, sm, L, KP, TV, tok0, nt, nt_ext, h, v0, gh, iph, cblk);
         }
         __syncthreads();
         // the raw stage is free again: fetch the next (earlier) block while this one is processed
-        if (c > 0) {
+        if (c > blk0) {
             const int t0n = t0 - TB;
             bwd_issue_ckpt(a, sm, L, st ^ 1, KP, TV, slot0 + c - 1, h, v0, tvw);
             if (a.aligned)
@@ -428,21 +469,23 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                         float2 hm = fmul2(hh, mu);
                         if (UNC) hm = ffma2(fmul2(dyv, qq[q]), fmul2(rr, rr), hm);
                         nGI[r][q] = ffma2(fn, nGI[r][q], hm);
-                        dqs[q] = ffma2(dy, mu, dqs[q]);
-                        if (UNC) Uk[q] = ffma2(dyv, rr, Uk[q]);
-                        Ak[q] = ffma2(GM[r][q], vv, Ak[q]);
-                        Bk[q] = ffma2(nGI[r][q], bv, Bk[q]);
-                        dva = ffma2(GM[r][q], kp[q], dva);
-                        dba = ffma2(nGI[r][q], kk[q], dba);
-                        Sa = ffma2(GM[r][q], P[j].M[r][q], Sa);
-                        Sb = ffma2(nGI[r][q], P[j].I[r][q], Sb);
-                        Sc = fadd2(Sc, nGI[r][q]);
+                        if (!CO) {
+                            dqs[q] = ffma2(dy, mu, dqs[q]);
+                            if (UNC) Uk[q] = ffma2(dyv, rr, Uk[q]);
+                            Ak[q] = ffma2(GM[r][q], vv, Ak[q]);
+                            Bk[q] = ffma2(nGI[r][q], bv, Bk[q]);
+                            dva = ffma2(GM[r][q], kp[q], dva);
+                            dba = ffma2(nGI[r][q], kk[q], dba);
+                            Sa = ffma2(GM[r][q], P[j].M[r][q], Sa);
+                            Sb = ffma2(nGI[r][q], P[j].I[r][q], Sb);
+                            Sc = fadd2(Sc, nGI[r][q]);
+                        }
                     }
                     red1[(j * RV + r) * 2 + 0] = dva.x + dva.y;
                     red1[(j * RV + r) * 2 + 1] = -(dba.x + dba.y);
                 }
                 // this row group's share of dq and dk for the token -> shared memory
-                {
+                if (!CO) {
                     float2* dst = kred2 + ((j * WV + wv) * 2) * KP2 + NP * kg;
                     const float2 sc2 = dup2(p.scale), m2 = dup2(-2.f);
 #pragma unroll
@@ -457,6 +500,7 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                 red2[j * 2 + 0] = (Sa.x + Sa.y) - (Sb.x + Sb.y) + iph * sc_;
                 red2[j * 2 + 1] = -sc_;
             }
+            if (CO) continue;  // carry-only pass: nothing but the state gradients is wanted
             // d_v-indexed sums over the KG lanes of a row; per-token scalars over the whole warp
             xreduce<NR1, KG>(red1, lane);
             {
@@ -497,6 +541,7 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
         }
 
         // ---- block epilogue: dv, db rows and the per-token scalars -----------------------------------
+        if (CO) continue;
         for (int i = tid; i < nt * TV; i += NTHR) {
             const int t = i / TV, r = i - t * TV;
             if (r < tvw) {
@@ -520,6 +565,22 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
             a.dip_part[e] = dip;
         }
         // the next iteration's first barrier orders these reads before the buffers are reused
+    }
+
+    // ---- gradient w.r.t. the segment's start state: decay the first token's totals once more ----------
+    if (a.rloc_M) {
+        const float f0 = fc2[0].x;  // f of the segment's first token (operands of the last processed block)
+#pragma unroll
+        for (int r = 0; r < RV; ++r) {
+            if (row0 + r < tvw) {
+#pragma unroll
+                for (int q = 0; q < NP; ++q) {
+                    const long long e = (seg_base + v0 + row0 + r) * KP + RK * kg + 2 * q;
+                    *reinterpret_cast<float2*>(a.rloc_M + e) = make_float2(f0 * GM[r][q].x, f0 * GM[r][q].y);
+                    *reinterpret_cast<float2*>(a.rloc_I + e) = make_float2(-f0 * nGI[r][q].x, -f0 * nGI[r][q].y);
+                }
+            }
+        }
     }
 }
 
@@ -664,44 +725,58 @@ BwdWorkspace bwd_workspace_layout(const palimpsa_problem& p) {
 }
 
 template <int RK, int KG, int RV, int W>
-static int launch_bwd_w(const BwdArgs& a, int tiles, cudaStream_t stream) {
+static int launch_bwd_w(const BwdArgs& a, int tiles, int num_seg, bool carry_only, cudaStream_t stream) {
     constexpr int VG = 32 / KG, TV = W * VG * RV;
     const palimpsa_problem& p = a.p;
     const bool unc = (p.flags & PALIMPSA_FLAG_UNCERTAINTY) != 0;
     const BwdSmem L = bwd_smem_layout(RK * KG, TV, RV * RK, 32 * W, W * VG, dtype_size(p.io_dtype), unc);
     if (L.total > 227 * 1024) return PALIMPSA_E_DIM;
-    dim3 grid(tiles, p.num_seqs * p.H, 1);
+    dim3 grid(tiles, p.num_seqs * p.H, num_seg);
     dim3 block(32 * W, 1, 1);
-    cudaError_t e;
-    if (unc) {
-        e = cudaFuncSetAttribute(bwd_kernel<RK, KG, RV, W, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
-        if (e != cudaSuccess) return PALIMPSA_E_LAUNCH;
-        bwd_kernel<RK, KG, RV, W, true><<<grid, block, L.total, stream>>>(a);
+#define PALIMPSA_BWD_LAUNCH(U, C)                                                                                 \
+    do {                                                                                                          \
+        if (cudaFuncSetAttribute(bwd_kernel<RK, KG, RV, W, U, C>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                                 L.total) != cudaSuccess)                                                         \
+            return PALIMPSA_E_LAUNCH;                                                                             \
+        bwd_kernel<RK, KG, RV, W, U, C><<<grid, block, L.total, stream>>>(a);                                     \
+    } while (0)
+    if (carry_only) {
+        if (unc) PALIMPSA_BWD_LAUNCH(true, true); else PALIMPSA_BWD_LAUNCH(false, true);
     } else {
-        e = cudaFuncSetAttribute(bwd_kernel<RK, KG, RV, W, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
-        if (e != cudaSuccess) return PALIMPSA_E_LAUNCH;
-        bwd_kernel<RK, KG, RV, W, false><<<grid, block, L.total, stream>>>(a);
+        if (unc) PALIMPSA_BWD_LAUNCH(true, false); else PALIMPSA_BWD_LAUNCH(false, false);
     }
+#undef PALIMPSA_BWD_LAUNCH
     return cudaGetLastError() == cudaSuccess ? PALIMPSA_OK : PALIMPSA_E_LAUNCH;
 }
 
 template <int RK, int KG, int RV>
-static int launch_bwd_t(const BwdArgs& a, int tiles, cudaStream_t stream) {
+static int launch_bwd_t(const BwdArgs& a, int tiles, int num_seg, bool carry_only, cudaStream_t stream) {
     const BwdConfig cfg = bwd_config(a.p);
-    if (cfg.W == 8) return launch_bwd_w<RK, KG, RV, 8>(a, tiles, stream);
-    if constexpr (RV > 1) return launch_bwd_w<RK, KG, RV, 4>(a, tiles, stream);
+    if (cfg.W == 8) return launch_bwd_w<RK, KG, RV, 8>(a, tiles, num_seg, carry_only, stream);
+    if constexpr (RV > 1) return launch_bwd_w<RK, KG, RV, 4>(a, tiles, num_seg, carry_only, stream);
     return PALIMPSA_E_DIM;
 }
 
 static bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
 
-int launch_bwd(const palimpsa_bwd_params* prm, cudaStream_t stream, int stages) {
+int launch_bwd(const palimpsa_bwd_params* prm, const palimpsa_segments* segs, bool carry_only, cudaStream_t stream,
+               int stages) {
     const palimpsa_problem& p = prm->p;
     const BwdWorkspace ws = bwd_workspace_layout(p);
     if (!ws.tiles) return PALIMPSA_E_DIM;
     char* base = reinterpret_cast<char*>(prm->workspace);
-    BwdArgs a;
+    BwdArgs a{};
     a.p = p;
+    int num_seg = 1;
+    if (segs) {
+        num_seg = segs->num_segments;
+        a.seg_len = segs->seg_len;
+        a.carry_M = carry_only ? nullptr : segs->carry_M;
+        a.carry_I = carry_only ? nullptr : segs->carry_I;
+        a.rloc_M = segs->rloc_M;
+        a.rloc_I = segs->rloc_I;
+    }
+    if (carry_only) stages = 1;
     a.d_o = prm->d_o;
     a.d_o_var = (p.flags & PALIMPSA_FLAG_UNCERTAINTY) ? prm->d_o_var : nullptr;
     a.ckpt_M = prm->ckpt_M;
@@ -719,14 +794,14 @@ int launch_bwd(const palimpsa_bwd_params* prm, cudaStream_t stream, int stages) 
                 (a.d_o_var == nullptr || aligned16(a.d_o_var)) && ((reinterpret_cast<uintptr_t>(p.gt) & 3) == 0);
     int rc = PALIMPSA_OK;
     if (stages & 1) switch (ws.KP) {
-        case 16: rc = launch_bwd_t<2, 8, 2>(a, ws.tiles, stream); break;
-        case 32: rc = launch_bwd_t<4, 8, 2>(a, ws.tiles, stream); break;
-        case 48: rc = launch_bwd_t<6, 8, 2>(a, ws.tiles, stream); break;
-        case 64: rc = launch_bwd_t<4, 16, 2>(a, ws.tiles, stream); break;
-        case 96: rc = launch_bwd_t<6, 16, 2>(a, ws.tiles, stream); break;
-        case 128: rc = launch_bwd_t<4, 32, 2>(a, ws.tiles, stream); break;
-        case 192: rc = launch_bwd_t<6, 32, 2>(a, ws.tiles, stream); break;
-        case 256: rc = launch_bwd_t<8, 32, 1>(a, ws.tiles, stream); break;
+        case 16: rc = launch_bwd_t<2, 8, 2>(a, ws.tiles, num_seg, carry_only, stream); break;
+        case 32: rc = launch_bwd_t<4, 8, 2>(a, ws.tiles, num_seg, carry_only, stream); break;
+        case 48: rc = launch_bwd_t<6, 8, 2>(a, ws.tiles, num_seg, carry_only, stream); break;
+        case 64: rc = launch_bwd_t<4, 16, 2>(a, ws.tiles, num_seg, carry_only, stream); break;
+        case 96: rc = launch_bwd_t<6, 16, 2>(a, ws.tiles, num_seg, carry_only, stream); break;
+        case 128: rc = launch_bwd_t<4, 32, 2>(a, ws.tiles, num_seg, carry_only, stream); break;
+        case 192: rc = launch_bwd_t<6, 32, 2>(a, ws.tiles, num_seg, carry_only, stream); break;
+        case 256: rc = launch_bwd_t<8, 32, 1>(a, ws.tiles, num_seg, carry_only, stream); break;
         default: return PALIMPSA_E_DIM;
     }
     if (rc != PALIMPSA_OK) return rc;
@@ -774,7 +849,7 @@ int launch_bwd_static(const palimpsa_bwd_params* prm, cudaStream_t stream) {
     palimpsa_bwd_params local = *prm;
     local.workspace = ptr;
     local.workspace_bytes = PALIMPSA_STATIC_SCRATCH_BYTES;
-    return launch_bwd(&local, stream, 3);
+    return launch_bwd(&local, nullptr, false, stream, 3);
 }
 
 }  // namespace palimpsa

@@ -34,6 +34,13 @@ struct FwdArgs {
     float* ckpt_M;
     float* ckpt_I;
     int aligned;  // 1: every io row is 16-byte aligned and a multiple of 16 bytes
+    // segments (gridDim.z of them per sequence; seg_len tokens each, a multiple of 16)
+    int seg_len;
+    const float* start_M;  // [N,G,H,V,KP] (M, I) at the start of every segment, or NULL
+    const float* start_I;
+    float* sum_M;          // summary mode: [N,G,H,V,KP] end state of the segment started from zero, (M, J) form
+    float* sum_J;
+    float* decay;          // summary mode: [N,G,H] product of f over the segment
 };
 
 struct FwdSmem {
@@ -165,7 +172,7 @@ __device__ __forceinline__ void fwd_convert(const FwdArgs& a, unsigned char* sm,
 // The recurrence over G consecutive tokens (no bounds checks: the caller only passes full groups),
 // followed by one batched reduction of the G*RV (x2 with uncertainty) output partials over the KG lanes
 // of the row group.  Kept free of conditionals on purpose: the state arrays M, I are updated in place.
-template <int RK, int KG, int RV, int TV, bool UNC, int G>
+template <int RK, int KG, int RV, int TV, bool UNC, bool SUM, int G>
 __device__ __forceinline__ void fwd_group(float2 (&M)[RV][RK / 4][2], float2 (&I)[RV][RK / 4][2], const float4* ks4,
                                           const float4* qs4, const float4* qqs4, const float2* vs2, const float2* bs2,
                                           const float4* fc, float* ys, float* yvs, int tg, int kg, int row0, int lane) {
@@ -198,10 +205,14 @@ __device__ __forceinline__ void fwd_group(float2 (&M)[RV][RK / 4][2], float2 (&I
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     M[r][j][e] = ffma2(ff, M[r][j][e], fmul2(vr[r], kp[e]));
-                    I[r][j][e] = ffma2(ff, I[r][j][e], ffma2(br[r], kkp[e], cc));
-                    const float2 rr = rcp2(I[r][j][e]);
-                    acc[r] = ffma2(fmul2(M[r][j][e], rr), qp[e], acc[r]);
-                    if (UNC) accv[r] = ffma2(rr, qqp[e], accv[r]);
+                    if (SUM) {  // J = f*J + b k^2: no prior term, no output
+                        I[r][j][e] = ffma2(ff, I[r][j][e], fmul2(br[r], kkp[e]));
+                    } else {
+                        I[r][j][e] = ffma2(ff, I[r][j][e], ffma2(br[r], kkp[e], cc));
+                        const float2 rr = rcp2(I[r][j][e]);
+                        acc[r] = ffma2(fmul2(M[r][j][e], rr), qp[e], acc[r]);
+                        if (UNC) accv[r] = ffma2(rr, qqp[e], accv[r]);
+                    }
                 }
             }
         }
@@ -211,6 +222,7 @@ __device__ __forceinline__ void fwd_group(float2 (&M)[RV][RK / 4][2], float2 (&I
             if (UNC) red[(jt * RV + r) * 2 + 1] = accv[r].x + accv[r].y;
         }
     }
+    if (SUM) return;
     xreduce<NRED, KG>(red, lane);
     constexpr int REM = NRED >= KG ? NRED / KG : 1;
     const int base = xreduce_index<NRED, KG>(lane);
@@ -227,7 +239,7 @@ __device__ __forceinline__ void fwd_group(float2 (&M)[RV][RK / 4][2], float2 (&I
     }
 }
 
-template <int RK, int KG, int RV, int W, bool UNC>
+template <int RK, int KG, int RV, int W, bool UNC, bool SUM>
 __global__ void __launch_bounds__(32 * W) fwd_kernel(const FwdArgs a) {
     constexpr int KP = RK * KG, VG = 32 / KG, J4 = RK / 4, TV = W * VG * RV, NTHR = 32 * W;
     constexpr int GF = 4;  // tokens whose outputs are reduced together
@@ -246,6 +258,11 @@ __global__ void __launch_bounds__(32 * W) fwd_kernel(const FwdArgs a) {
     const float gh = p.g[h], iph = p.Ip[h];
     const int K = p.K, V = p.V;
     const bool vecK = (K % 4) == 0;
+    // this CTA's segment of the sequence: tokens [s0, s1)
+    const int g = blockIdx.z, G = gridDim.z;
+    const int s0 = a.seg_len > 0 ? min(len, g * a.seg_len) : 0;
+    const int s1 = a.seg_len > 0 ? min(len, s0 + a.seg_len) : len;
+    const long long seg_base = (((long long)n * G + g) * p.H + h) * V;  // row index into [N,G,H,V,KP] buffers
 
     // ---- state registers ------------------------------------------------------------------
     float2 M[RV][J4][2], I[RV][J4][2];
@@ -258,7 +275,15 @@ __global__ void __launch_bounds__(32 * W) fwd_kernel(const FwdArgs a) {
             const int kc = 4 * (j * KG + kg);
             float4 m4 = make_float4(0.f, 0.f, 0.f, 0.f);
             float4 i4 = make_float4(1.f, 1.f, 1.f, 1.f);
-            if (vrow < V && kc < K) {
+            if (SUM) {
+                i4 = m4;  // summaries start from M = 0, J = 0
+            } else if (a.start_M) {
+                if (vrow < V) {
+                    const long long e = (seg_base + vrow) * KP + kc;
+                    m4 = *reinterpret_cast<const float4*>(a.start_M + e);
+                    i4 = *reinterpret_cast<const float4*>(a.start_I + e);
+                }
+            } else if (vrow < V && kc < K) {
                 if (p.init_mu) {
                     const long long e = (st_base + vrow) * K + kc;
                     float4 mu4;
@@ -285,8 +310,9 @@ __global__ void __launch_bounds__(32 * W) fwd_kernel(const FwdArgs a) {
         }
     }
 
-    const int nblk = (len + TB - 1) / TB;
+    const int blk0 = s0 / TB, nblk = s1 > s0 ? (s1 + TB - 1) / TB : blk0;  // blocks [blk0, nblk) of the sequence
     const long long slot0 = seq_first_slot(p, n);
+    float Pdecay = 1.f;
     const float4* qs4 = reinterpret_cast<const float4*>(sm + L.qs);
     const float4* ks4 = reinterpret_cast<const float4*>(sm + L.ks);
     const float4* qqs4 = reinterpret_cast<const float4*>(sm + L.qqs);
@@ -297,19 +323,20 @@ __global__ void __launch_bounds__(32 * W) fwd_kernel(const FwdArgs a) {
     float* yvs = reinterpret_cast<float*>(sm + L.yvs);
     unsigned char* raw = sm + L.raw;
 
-    if (a.aligned && nblk > 0) {
-        fwd_issue(a, raw, L, es, KP, TV, bos, min(TB, len), h, v0, tvw);
+    if (a.aligned && nblk > blk0) {
+        fwd_issue(a, raw + (blk0 & 1) * L.raw_stage, L, es, KP, TV, (long long)bos + blk0 * TB, min(TB, s1 - blk0 * TB),
+                  h, v0, tvw);
         cp_async_commit();
     }
 
-    for (int blk = 0; blk < nblk; ++blk) {
+    for (int blk = blk0; blk < nblk; ++blk) {
         const int t0 = blk * TB;
-        const int nt = min(TB, len - t0);
+        const int nt = min(TB, s1 - t0);
         const long long tok0 = (long long)bos + t0;
         unsigned char* stage = raw + (blk & 1) * L.raw_stage;
         if (a.aligned) {
             if (blk + 1 < nblk) {
-                fwd_issue(a, raw + ((blk + 1) & 1) * L.raw_stage, L, es, KP, TV, tok0 + TB, min(TB, len - t0 - TB), h,
+                fwd_issue(a, raw + ((blk + 1) & 1) * L.raw_stage, L, es, KP, TV, tok0 + TB, min(TB, s1 - t0 - TB), h,
                           v0, tvw);
                 cp_async_commit();
                 cp_async_wait<1>();
@@ -335,8 +362,10 @@ __global__ void __launch_bounds__(32 * W) fwd_kernel(const FwdArgs a) {
         }
         __syncthreads();
 
+        if (SUM && tid == 0)
+            for (int t = 0; t < nt; ++t) Pdecay *= fc[t].x;
         // ---- checkpoint: state before the first token of this block ---------------------------
-        if (a.ckpt_M) {
+        if (!SUM && a.ckpt_M) {
             const long long cbase = ((slot0 + blk) * p.H + h) * V;
 #pragma unroll
             for (int r = 0; r < RV; ++r) {
@@ -358,13 +387,14 @@ __global__ void __launch_bounds__(32 * W) fwd_kernel(const FwdArgs a) {
         int tg = 0;
 #pragma unroll 1
         for (; tg + GF <= nt; tg += GF)
-            fwd_group<RK, KG, RV, TV, UNC, GF>(M, I, ks4, qs4, qqs4, vs2, bs2, fc, ys, yvs, tg, kg, row0, lane);
+            fwd_group<RK, KG, RV, TV, UNC, SUM, GF>(M, I, ks4, qs4, qqs4, vs2, bs2, fc, ys, yvs, tg, kg, row0, lane);
 #pragma unroll 1
         for (; tg < nt; ++tg)
-            fwd_group<RK, KG, RV, TV, UNC, 1>(M, I, ks4, qs4, qqs4, vs2, bs2, fc, ys, yvs, tg, kg, row0, lane);
+            fwd_group<RK, KG, RV, TV, UNC, SUM, 1>(M, I, ks4, qs4, qqs4, vs2, bs2, fc, ys, yvs, tg, kg, row0, lane);
         __syncthreads();
 
         // ---- write the block's outputs -----------------------------------------------------------
+        if (!SUM)
         for (int i = tid; i < nt * TV; i += NTHR) {
             const int t = i / TV, r = i - t * TV;
             if (r < tvw) {
@@ -375,8 +405,26 @@ __global__ void __launch_bounds__(32 * W) fwd_kernel(const FwdArgs a) {
         }
     }
 
-    // ---- final state in the API's (mu, I) form ---------------------------------------------------
-    if (a.final_mu) {
+    if (SUM) {  // segment summary: end state from a zero start, and the segment's total decay
+#pragma unroll
+        for (int r = 0; r < RV; ++r) {
+            const int vrow = v0 + row0 + r;
+            if (vrow < V) {
+#pragma unroll
+                for (int j = 0; j < J4; ++j) {
+                    const long long e = (seg_base + vrow) * KP + 4 * (j * KG + kg);
+                    *reinterpret_cast<float4*>(a.sum_M + e) =
+                        make_float4(M[r][j][0].x, M[r][j][0].y, M[r][j][1].x, M[r][j][1].y);
+                    *reinterpret_cast<float4*>(a.sum_J + e) =
+                        make_float4(I[r][j][0].x, I[r][j][0].y, I[r][j][1].x, I[r][j][1].y);
+                }
+            }
+        }
+        if (tid == 0 && blockIdx.x == 0) a.decay[((long long)n * G + g) * p.H + h] = Pdecay;
+        return;
+    }
+    // ---- final state in the API's (mu, I) form: written by the segment that holds the last token -----
+    if (a.final_mu && s1 == len && (s0 < len || g == 0)) {
 #pragma unroll
         for (int r = 0; r < RV; ++r) {
             const int vrow = v0 + row0 + r;
@@ -411,41 +459,48 @@ __global__ void __launch_bounds__(32 * W) fwd_kernel(const FwdArgs a) {
 // Host side
 // -------------------------------------------------------------------------------------------------
 template <int RK, int KG, int RV, int W>
-static int launch_fwd_w(const FwdArgs& a, cudaStream_t stream) {
+static int launch_fwd_w(const FwdArgs& a, int num_seg, bool summary, cudaStream_t stream) {
     constexpr int VG = 32 / KG, TV = W * VG * RV;
     const palimpsa_problem& p = a.p;
-    const bool unc = (p.flags & PALIMPSA_FLAG_UNCERTAINTY) != 0;
+    const bool unc = !summary && (p.flags & PALIMPSA_FLAG_UNCERTAINTY) != 0;
     const FwdSmem L = fwd_smem_layout(RK * KG, TV, dtype_size(p.io_dtype), unc);
-    dim3 grid((p.V + TV - 1) / TV, p.num_seqs * p.H, 1);
+    dim3 grid((p.V + TV - 1) / TV, p.num_seqs * p.H, num_seg);
     dim3 block(32 * W, 1, 1);
     cudaError_t e;
-    if (unc) {
-        e = cudaFuncSetAttribute(fwd_kernel<RK, KG, RV, W, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+    if (summary) {
+        e = cudaFuncSetAttribute(fwd_kernel<RK, KG, RV, W, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 L.total);
         if (e != cudaSuccess) return PALIMPSA_E_LAUNCH;
-        fwd_kernel<RK, KG, RV, W, true><<<grid, block, L.total, stream>>>(a);
+        fwd_kernel<RK, KG, RV, W, false, true><<<grid, block, L.total, stream>>>(a);
+    } else if (unc) {
+        e = cudaFuncSetAttribute(fwd_kernel<RK, KG, RV, W, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 L.total);
+        if (e != cudaSuccess) return PALIMPSA_E_LAUNCH;
+        fwd_kernel<RK, KG, RV, W, true, false><<<grid, block, L.total, stream>>>(a);
     } else {
-        e = cudaFuncSetAttribute(fwd_kernel<RK, KG, RV, W, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+        e = cudaFuncSetAttribute(fwd_kernel<RK, KG, RV, W, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 L.total);
         if (e != cudaSuccess) return PALIMPSA_E_LAUNCH;
-        fwd_kernel<RK, KG, RV, W, false><<<grid, block, L.total, stream>>>(a);
+        fwd_kernel<RK, KG, RV, W, false, false><<<grid, block, L.total, stream>>>(a);
     }
     return cudaGetLastError() == cudaSuccess ? PALIMPSA_OK : PALIMPSA_E_LAUNCH;
 }
 
 // Warps per CTA: WMAX, or fewer when d_v is short (the row tile stays a multiple of 8 rows).
 template <int RK, int KG, int RV, int WMAX>
-static int launch_fwd_t(const FwdArgs& a, cudaStream_t stream) {
+static int launch_fwd_t(const FwdArgs& a, int num_seg, bool summary, cudaStream_t stream) {
     constexpr int RPW = (32 / KG) * RV;
     if constexpr (WMAX >= 4 && (RPW * (WMAX / 4)) % 8 == 0)
-        if (a.p.V <= RPW * (WMAX / 4)) return launch_fwd_w<RK, KG, RV, WMAX / 4>(a, stream);
+        if (a.p.V <= RPW * (WMAX / 4)) return launch_fwd_w<RK, KG, RV, WMAX / 4>(a, num_seg, summary, stream);
     if constexpr (WMAX >= 2 && (RPW * (WMAX / 2)) % 8 == 0)
-        if (a.p.V <= RPW * (WMAX / 2)) return launch_fwd_w<RK, KG, RV, WMAX / 2>(a, stream);
-    return launch_fwd_w<RK, KG, RV, WMAX>(a, stream);
+        if (a.p.V <= RPW * (WMAX / 2)) return launch_fwd_w<RK, KG, RV, WMAX / 2>(a, num_seg, summary, stream);
+    return launch_fwd_w<RK, KG, RV, WMAX>(a, num_seg, summary, stream);
 }
 
 static bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
 
-int launch_fwd(const palimpsa_fwd_params* prm, cudaStream_t stream) {
-    FwdArgs a;
+int launch_fwd(const palimpsa_fwd_params* prm, const palimpsa_segments* segs, bool summary, cudaStream_t stream) {
+    FwdArgs a{};
     a.p = prm->p;
     a.o = prm->o;
     a.o_var = prm->o_var;
@@ -453,6 +508,19 @@ int launch_fwd(const palimpsa_fwd_params* prm, cudaStream_t stream) {
     a.final_I = prm->final_I;
     a.ckpt_M = prm->ckpt_M;
     a.ckpt_I = prm->ckpt_I;
+    int num_seg = 1;
+    if (segs) {
+        num_seg = segs->num_segments;
+        a.seg_len = segs->seg_len;
+        if (summary) {
+            a.sum_M = segs->sum_M;
+            a.sum_J = segs->sum_J;
+            a.decay = segs->decay;
+        } else {
+            a.start_M = segs->start_M;
+            a.start_I = segs->start_I;
+        }
+    }
     const palimpsa_problem& p = a.p;
     const int es = dtype_size(p.io_dtype);
     a.aligned = ((p.K * es) % 16 == 0) && ((p.V * es) % 16 == 0) && aligned16(p.q) && aligned16(p.k) &&
@@ -463,19 +531,19 @@ int launch_fwd(const palimpsa_fwd_params* prm, cudaStream_t stream) {
         return e ? atoi(e) : 0;
     }();
     switch (palimpsa_padded_k(p.K)) {
-        case 16: return launch_fwd_t<8, 2, 2, 2>(a, stream);
-        case 32: return launch_fwd_t<8, 4, 2, 4>(a, stream);
-        case 48: return launch_fwd_t<12, 4, 2, 4>(a, stream);
-        case 64: return launch_fwd_t<16, 4, 2, 2>(a, stream);
-        case 96: return launch_fwd_t<12, 8, 2, 4>(a, stream);
+        case 16: return launch_fwd_t<8, 2, 2, 2>(a, num_seg, summary, stream);
+        case 32: return launch_fwd_t<8, 4, 2, 4>(a, num_seg, summary, stream);
+        case 48: return launch_fwd_t<12, 4, 2, 4>(a, num_seg, summary, stream);
+        case 64: return launch_fwd_t<16, 4, 2, 2>(a, num_seg, summary, stream);
+        case 96: return launch_fwd_t<12, 8, 2, 4>(a, num_seg, summary, stream);
         case 128:
-            if (cfg == 1) return launch_fwd_t<16, 8, 2, 4>(a, stream);
-            if (cfg == 2) return launch_fwd_t<4, 32, 2, 4>(a, stream);
-            if (cfg == 3) return launch_fwd_t<4, 32, 4, 4>(a, stream);
-            if (cfg == 4) return launch_fwd_t<8, 16, 4, 4>(a, stream);
-            return launch_fwd_t<8, 16, 2, 4>(a, stream);
-        case 192: return launch_fwd_t<12, 16, 2, 4>(a, stream);
-        case 256: return launch_fwd_t<16, 16, 2, 4>(a, stream);
+            if (cfg == 1) return launch_fwd_t<16, 8, 2, 4>(a, num_seg, summary, stream);
+            if (cfg == 2) return launch_fwd_t<4, 32, 2, 4>(a, num_seg, summary, stream);
+            if (cfg == 3) return launch_fwd_t<4, 32, 4, 4>(a, num_seg, summary, stream);
+            if (cfg == 4) return launch_fwd_t<8, 16, 4, 4>(a, num_seg, summary, stream);
+            return launch_fwd_t<8, 16, 2, 4>(a, num_seg, summary, stream);
+        case 192: return launch_fwd_t<12, 16, 2, 4>(a, num_seg, summary, stream);
+        case 256: return launch_fwd_t<16, 16, 2, 4>(a, num_seg, summary, stream);
         default: return PALIMPSA_E_DIM;
     }
 }

@@ -7,15 +7,24 @@
 
 namespace palimpsa {
 
-// Enqueue the forward kernel (fwd.cu).  Parameters are assumed validated.
-int launch_fwd(const palimpsa_fwd_params* prm, cudaStream_t stream);
+// Enqueue the forward kernel (fwd.cu).  Parameters are assumed validated.  With `segs` every sequence is
+// cut into segs->num_segments segments that run as separate CTAs: `summary` = false starts each from
+// segs->start_M/start_I; `summary` = true computes the zero-start end state and decay of every segment.
+int launch_fwd(const palimpsa_fwd_params* prm, const palimpsa_segments* segs, bool summary, cudaStream_t stream);
 
 // Single-token decode step (decode.cu): dedicated HBM-bound kernel, when it covers the call.
 bool decode_supported(const palimpsa_fwd_params* prm);
 int launch_decode(const palimpsa_fwd_params* prm, cudaStream_t stream);
 
 // Backward (bwd.cu): main kernel (stages bit 0) + the two finishing kernels (bit 1).
-int launch_bwd(const palimpsa_bwd_params* prm, cudaStream_t stream, int stages);
+int launch_bwd(const palimpsa_bwd_params* prm, const palimpsa_segments* segs, bool carry_only, cudaStream_t stream,
+               int stages);
+
+// Boundary scans over segments (segments.cu).
+int launch_combine_fwd(const palimpsa_problem& p, const palimpsa_segments& segs, const float* in_M, const float* in_J,
+                       float* out_M, float* out_J, cudaStream_t stream);
+int launch_combine_bwd(const palimpsa_problem& p, const palimpsa_segments& segs, const float* in_M, const float* in_I,
+                       float* out_M, float* out_I, cudaStream_t stream);
 
 // Backward whose scratch is the library's own fixed device array (bwd.cu).
 int launch_bwd_static(const palimpsa_bwd_params* prm, cudaStream_t stream);

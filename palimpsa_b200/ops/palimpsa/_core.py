@@ -69,11 +69,43 @@ def _chunk_offsets(cu_seqlens: Tensor) -> Tensor:
     return (torch.cumsum(nblk, 0) - nblk).to(torch.int32)
 
 
+def plan_segments(N: int, T: int, H: int, K: int, V: int) -> int:
+    """How many segments to cut every sequence into on one GPU.  Segments cost an extra summary pass
+    (and an extra state-gradient pass in backward), so they are only used when the (sequence, head,
+    row-tile) grid alone would leave most of the 148 SMs idle, e.g. one very long sequence."""
+    ctas = N * H * ((V + 15) // 16)
+    if ctas >= 148 or T < 1024:
+        return 1
+    return max(1, min((296 + ctas - 1) // ctas, T // 512))
+
+
+def segment_len(T: int, G: int) -> int:
+    per = (T + G - 1) // G
+    return max(L.CKPT_INTERVAL, (per + L.CKPT_INTERVAL - 1) // L.CKPT_INTERVAL * L.CKPT_INTERVAL)
+
+
+def make_segments(N, G, seg_len, H, V, K, dev, fwd: bool, with_rloc=True):
+    """Allocates the [N,G,H,V,KP] boundary buffers and returns (ctypes struct, dict of tensors)."""
+    KP = padded_k(K)
+    f32 = dict(dtype=torch.float32, device=dev)
+    sg = L.Segments()
+    sg.num_segments, sg.seg_len = G, seg_len
+    t = {}
+    names = ("sum_M", "sum_J", "start_M", "start_I") if fwd else ("carry_M", "carry_I", "rloc_M", "rloc_I")
+    for n in names:
+        t[n] = torch.empty(N, G, H, V, KP, **f32)
+        setattr(sg, n, t[n].data_ptr())
+    if fwd:
+        t["decay"] = torch.empty(N, G, H, **f32)
+        sg.decay = t["decay"].data_ptr()
+    return sg, t
+
+
 @torch.library.custom_op("palimpsa_b200::fwd", mutates_args=(), device_types="cuda")
 def fwd_op(q: Tensor, k: Tensor, v: Tensor, b: Tensor, gt: Tensor, g: Tensor, Ip: Tensor,
            init_mu: Optional[Tensor], init_I: Optional[Tensor], cu_seqlens: Optional[Tensor],
-           scale: float, uncertainty: bool, save_ckpt: bool, want_final: bool,
-           recurrent: bool) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+           scale: float, uncertainty: bool, save_ckpt: bool, want_final: bool, recurrent: bool,
+           num_segments: int) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
     _require_cuda(q, k, v, b, gt, g, Ip, init_mu, init_I, cu_seqlens)
     lib = L.lib()
     B, T, H, K = q.shape
@@ -102,16 +134,29 @@ def fwd_op(q: Tensor, k: Tensor, v: Tensor, b: Tensor, gt: Tensor, g: Tensor, Ip
         prm.o, prm.o_var = _ptr(o), _ptr(o_var)
         prm.final_mu, prm.final_I = _ptr(fmu), _ptr(fI)
         prm.ckpt_M, prm.ckpt_I = _ptr(ckM), _ptr(ckI)
-        fn = lib.palimpsa_recurrent_fwd if recurrent else lib.palimpsa_chunk_fwd
-        L.check(fn(C.byref(prm), _stream(q)), "palimpsa forward")
+        decay = None
+        if num_segments > 1 and cu_seqlens is None and T > 0:
+            # summaries of every segment -> boundary scan -> all segments run side by side
+            sg, bufs = make_segments(N, num_segments, segment_len(T, num_segments), H, V, K, dev, fwd=True)
+            st = _stream(q)
+            L.check(lib.palimpsa_segment_summary(C.byref(prm.p), C.byref(sg), st), "palimpsa segment summary")
+            L.check(lib.palimpsa_cp_combine(C.byref(prm.p), C.byref(sg), None, None, None, None, st),
+                    "palimpsa boundary scan")
+            L.check(lib.palimpsa_chunk_fwd_segments(C.byref(prm), C.byref(sg), st), "palimpsa forward (segments)")
+            decay = bufs["decay"]
+        else:
+            fn = lib.palimpsa_recurrent_fwd if recurrent else lib.palimpsa_chunk_fwd
+            L.check(fn(C.byref(prm), _stream(q)), "palimpsa forward")
     e = q.new_empty(0, dtype=torch.float32)
     return (o, o_var, fmu if want_final else e, fI if want_final else e.clone(),
             ckM if save_ckpt else e.clone(), ckI if save_ckpt else e.clone(),
-            coff if coff is not None else q.new_empty(0, dtype=torch.int32))
+            coff if coff is not None else q.new_empty(0, dtype=torch.int32),
+            decay if decay is not None else e.clone())
 
 
 @fwd_op.register_fake
-def _(q, k, v, b, gt, g, Ip, init_mu, init_I, cu_seqlens, scale, uncertainty, save_ckpt, want_final, recurrent):
+def _(q, k, v, b, gt, g, Ip, init_mu, init_I, cu_seqlens, scale, uncertainty, save_ckpt, want_final, recurrent,
+      num_segments):
     B, T, H, K = q.shape
     V = v.shape[-1]
     N = B if cu_seqlens is None else cu_seqlens.numel() - 1
@@ -122,14 +167,16 @@ def _(q, k, v, b, gt, g, Ip, init_mu, init_I, cu_seqlens, scale, uncertainty, sa
     fI = q.new_empty((N, H, V, K) if want_final else (0,), **f32)
     cs = (_ckpt_slots(B * T, N), H, V, padded_k(K)) if save_ckpt else (0,)
     coff = q.new_empty((N,) if cu_seqlens is not None else (0,), dtype=torch.int32)
-    return o, o_var, fmu, fI, q.new_empty(cs, **f32), q.new_empty(cs, **f32), coff
+    seg = num_segments > 1 and cu_seqlens is None and T > 0
+    decay = q.new_empty((N, num_segments, H) if seg else (0,), **f32)
+    return o, o_var, fmu, fI, q.new_empty(cs, **f32), q.new_empty(cs, **f32), coff, decay
 
 
 @torch.library.custom_op("palimpsa_b200::bwd", mutates_args=(), device_types="cuda")
 def bwd_op(do: Tensor, do_var: Optional[Tensor], q: Tensor, k: Tensor, v: Tensor, b: Tensor, gt: Tensor, g: Tensor,
            Ip: Tensor, cu_seqlens: Optional[Tensor], chunk_offsets: Optional[Tensor], ckpt_M: Tensor, ckpt_I: Tensor,
-           scale: float, explicit_init: bool,
-           recurrent: bool) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+           scale: float, explicit_init: bool, recurrent: bool,
+           seg_decay: Optional[Tensor]) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
     _require_cuda(do, do_var, q, k, v, b, gt, g, Ip, cu_seqlens, ckpt_M, ckpt_I)
     lib = L.lib()
     B, T, H, K = q.shape
@@ -150,13 +197,27 @@ def bwd_op(do: Tensor, do_var: Optional[Tensor], q: Tensor, k: Tensor, v: Tensor
         prm.dq, prm.dk, prm.dv, prm.db = _ptr(dq), _ptr(dk), _ptr(dv), _ptr(db)
         prm.dgt, prm.dg, prm.dIp = _ptr(dgt), _ptr(dg), _ptr(dIp)
         prm.workspace, prm.workspace_bytes = ws.data_ptr(), ws.numel()
-        fn = lib.palimpsa_recurrent_bwd if recurrent else lib.palimpsa_chunk_bwd
-        L.check(fn(C.byref(prm), _stream(q)), "palimpsa backward")
+        if seg_decay is not None and seg_decay.numel() > 0:
+            # state-gradient pass per segment -> reverse boundary scan -> full backward per segment
+            G = seg_decay.shape[1]
+            V = v.shape[-1]
+            sg, bufs = make_segments(B, G, segment_len(T, G), H, V, K, dev, fwd=False)
+            sg.decay = seg_decay.data_ptr()
+            st = _stream(q)
+            L.check(lib.palimpsa_chunk_bwd_segments(C.byref(prm), C.byref(sg), 1, st), "palimpsa backward (carry pass)")
+            L.check(lib.palimpsa_cp_combine_bwd(C.byref(prm.p), C.byref(sg), None, None, None, None, st),
+                    "palimpsa boundary scan (backward)")
+            sg.rloc_M = sg.rloc_I = None
+            L.check(lib.palimpsa_chunk_bwd_segments(C.byref(prm), C.byref(sg), 0, st), "palimpsa backward (segments)")
+        else:
+            fn = lib.palimpsa_recurrent_bwd if recurrent else lib.palimpsa_chunk_bwd
+            L.check(fn(C.byref(prm), _stream(q)), "palimpsa backward")
     return dq, dk, dv, db, dgt, dg, dIp
 
 
 @bwd_op.register_fake
-def _(do, do_var, q, k, v, b, gt, g, Ip, cu_seqlens, chunk_offsets, ckpt_M, ckpt_I, scale, explicit_init, recurrent):
+def _(do, do_var, q, k, v, b, gt, g, Ip, cu_seqlens, chunk_offsets, ckpt_M, ckpt_I, scale, explicit_init, recurrent,
+      seg_decay):
     B, T, H, K = q.shape
     f32 = dict(dtype=torch.float32, device=q.device)
     return (torch.empty_like(q), torch.empty_like(k), torch.empty_like(v), torch.empty_like(b),
@@ -164,19 +225,20 @@ def _(do, do_var, q, k, v, b, gt, g, Ip, cu_seqlens, chunk_offsets, ckpt_M, ckpt
 
 
 def _setup_context(ctx, inputs, output):
-    (q, k, v, b, gt, g, Ip, init_mu, init_I, cu_seqlens, scale, uncertainty, save_ckpt, want_final, recurrent) = inputs
-    o, o_var, fmu, fI, ckM, ckI, coff = output
+    (q, k, v, b, gt, g, Ip, init_mu, init_I, cu_seqlens, scale, uncertainty, save_ckpt, want_final, recurrent,
+     num_segments) = inputs
+    o, o_var, fmu, fI, ckM, ckI, coff, decay = output
     ctx.scale, ctx.uncertainty, ctx.recurrent = scale, uncertainty, recurrent
     ctx.explicit_init = init_mu is not None
     ctx.has_ckpt = save_ckpt
     ctx.varlen = cu_seqlens is not None
-    ctx.save_for_backward(q, k, v, b, gt, g, Ip, cu_seqlens, coff, ckM, ckI)
+    ctx.save_for_backward(q, k, v, b, gt, g, Ip, cu_seqlens, coff, ckM, ckI, decay)
 
 
-def _backward(ctx, do, do_var, dfmu, dfI, _dckM, _dckI, _dcoff):
+def _backward(ctx, do, do_var, dfmu, dfI, _dckM, _dckI, _dcoff, _ddecay):
     # Gradients reaching the final states are ignored and initial states get none, as in the
     # reference (chunk_palimpsa_forgetting_scalar.py:522, :617-620: truncated BPTT across calls).
-    q, k, v, b, gt, g, Ip, cu_seqlens, coff, ckM, ckI = ctx.saved_tensors
+    q, k, v, b, gt, g, Ip, cu_seqlens, coff, ckM, ckI, decay = ctx.saved_tensors
     if not ctx.has_ckpt:
         raise RuntimeError("palimpsa_b200: backward needs the forward's checkpoints (forward ran with save_ckpt=False)")
     if do is None:
@@ -190,15 +252,15 @@ def _backward(ctx, do, do_var, dfmu, dfI, _dckM, _dckI, _dcoff):
         do_var = None
     dq, dk, dv, db, dgt, dg, dIp = bwd_op(do, do_var, q, k, v, b, gt, g, Ip, cu_seqlens if ctx.varlen else None,
                                           coff if ctx.varlen else None, ckM, ckI, ctx.scale, ctx.explicit_init,
-                                          ctx.recurrent)
-    return dq, dk, dv, db, dgt, dg, dIp, None, None, None, None, None, None, None, None
+                                          ctx.recurrent, decay if decay.numel() > 0 else None)
+    return dq, dk, dv, db, dgt, dg, dIp, None, None, None, None, None, None, None, None, None
 
 
 fwd_op.register_autograd(_backward, setup_context=_setup_context)
 
 
 def run(q, k, v, b, gt, g, Ip, initial_mu_state, initial_I_state, scale, output_final_state, output_uncertainty,
-        cu_seqlens, recurrent: bool, out_dtype):
+        cu_seqlens, recurrent: bool, out_dtype, num_segments: Optional[int] = None):
     """Shared body of chunk_palimpsa / fused_recurrent_palimpsa: checks, dtype policy, op call, packing."""
     if q.dim() != 4 or k.shape != q.shape or v.dim() != 4 or b.shape != v.shape or v.shape[:3] != q.shape[:3]:
         raise ValueError("expected q,k [B,T,H,K] and v,b [B,T,H,V]")
@@ -225,9 +287,11 @@ def run(q, k, v, b, gt, g, Ip, initial_mu_state, initial_I_state, scale, output_
     q, k, v, b = [x.to(io).contiguous() for x in (q, k, v, b)]
     gt, g, Ip = [x.float().contiguous() for x in (gt, g, Ip)]
     save_ckpt = torch.is_grad_enabled() and any(x.requires_grad for x in (q, k, v, b, gt, g, Ip))
-    o, o_var, fmu, fI, _, _, _ = fwd_op(q, k, v, b, gt, g, Ip, initial_mu_state, initial_I_state, cu_seqlens,
-                                        float(scale), bool(output_uncertainty), save_ckpt, bool(output_final_state),
-                                        recurrent)
+    if num_segments is None:
+        num_segments = 1 if cu_seqlens is not None else plan_segments(N, T, H, K, V)
+    o, o_var, fmu, fI, _, _, _, _ = fwd_op(q, k, v, b, gt, g, Ip, initial_mu_state, initial_I_state, cu_seqlens,
+                                           float(scale), bool(output_uncertainty), save_ckpt, bool(output_final_state),
+                                           recurrent, int(num_segments))
     if out_dtype is not None and out_dtype != o.dtype:
         o = o.to(out_dtype)
     out = (o, o_var) if output_uncertainty else o

@@ -6,7 +6,7 @@ from . import _core
 
 
 def chunk_palimpsa(q, k, v, b, gt, g, Ip, initial_mu_state=None, initial_I_state=None, scale=None, chunk_size=16,
-                   output_final_state=False, output_uncertainty=False, cu_seqlens=None):
+                   output_final_state=False, output_uncertainty=False, cu_seqlens=None, *, num_segments=None):
     """Palimpsa operator for training and prefill; differentiable w.r.t. q, k, v, b, gt, g, Ip.
 
     Arguments and return value follow the reference: ``q,k [B,T,H,K]``, ``v,b [B,T,H,V]``,
@@ -19,10 +19,14 @@ def chunk_palimpsa(q, k, v, b, gt, g, Ip, initial_mu_state=None, initial_I_state
     palimpsa/layers/palimpsa.py:309) whatever is asked.  The uncertainty output uses ``scale`` to
     the first power like the reference's kernels (:204), not ``scale**2`` like ``palimpsa_ref``.
     Unlike the reference kernel (:418), ``dIp`` is exact when an initial state is given.
+
+    ``num_segments`` (keyword-only, not in the reference): cut every sequence into that many segments
+    that run side by side (boundary states from a summary pass and a scan); default: chosen from the
+    problem size, 1 unless the grid would leave most SMs idle.  Ignored with ``cu_seqlens``.
     """
     if scale is None:
         scale = q.shape[-1] ** -0.5
     if cu_seqlens is not None and q.shape[0] != 1:
         raise ValueError(f"Batch size must be 1 for Varlen, got {q.shape[0]}")
     return _core.run(q, k, v, b, gt, g, Ip, initial_mu_state, initial_I_state, scale, output_final_state,
-                     output_uncertainty, cu_seqlens, recurrent=False, out_dtype=q.dtype)
+                     output_uncertainty, cu_seqlens, recurrent=False, out_dtype=q.dtype, num_segments=num_segments)

@@ -1,0 +1,66 @@
+"""Segment-parallel execution on one GPU: sequences cut into segments that run side by side must give
+the same outputs, final states and gradients as the float64 oracle (and as the unsegmented op)."""
+import pytest
+import torch
+
+from oracle import palimpsa_oracle as orc
+from tests.gpu_util import DEV, compare, run_oracle
+from tests.helpers import TOL_BF16, TOL_FP32
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(inp, G, unc=False, mu0=None, I0=None):
+    from palimpsa_b200.ops import chunk_palimpsa
+    names = ("q", "k", "v", "b", "gt", "g", "Ip")
+    leaves = {n: inp[n].to(DEV).clone().requires_grad_(True) for n in names}
+    kw = dict(output_final_state=True, output_uncertainty=unc, num_segments=G)
+    if mu0 is not None:
+        kw.update(initial_mu_state=mu0.to(DEV), initial_I_state=I0.to(DEV))
+    out, fmu, fI = chunk_palimpsa(*[leaves[n] for n in names], **kw)
+    res = {"final_mu": fmu, "final_I": fI}
+    if unc:
+        res["o"], res["o_var"] = out
+    else:
+        res["o"] = out
+    loss = (res["o"].float() * inp["do"].to(DEV).float()).sum()
+    if unc:
+        loss = loss + (res["o_var"].float() * inp["do_var"].to(DEV).float()).sum()
+    loss.backward()
+    for n in names:
+        res["d" + n] = leaves[n].grad
+    torch.cuda.synchronize()
+    return {k: v.detach().cpu() for k, v in res.items()}
+
+
+@pytest.mark.parametrize("T,G", [(200, 3), (64, 4), (131, 2), (50, 7)])
+def test_segments_fp32(T, G):
+    inp = orc.make_inputs(T + G, B=2, T=T, H=2, K=64, V=40)
+    got = _run(inp, G, unc=True)
+    ref = run_oracle(inp, unc=True)
+    compare(got, ref, TOL_FP32, what=f"segments T={T} G={G}")
+
+
+def test_segments_with_initial_state_and_slow_decay():
+    inp = orc.make_inputs(3, B=1, T=300, H=3, K=32, V=32)
+    inp["gt"] = inp["gt"] * 0.02            # decays 0.95 .. 0.9998: boundary states matter over long ranges
+    mu0, I0 = orc.make_states(4, 1, 3, 32, 32, inp["Ip"])
+    got = _run(inp, 5, mu0=mu0, I0=I0)
+    ref = run_oracle(inp, mu0=mu0, I0=I0)
+    compare(got, ref, TOL_FP32, what="segments + init")
+
+
+def test_segments_bf16_match_unsegmented():
+    inp = orc.make_inputs(9, B=1, T=2048, H=2, K=128, V=128, dtype=torch.bfloat16)
+    inp["gt"] = inp["gt"] * 0.05
+    a = _run(inp, 1)
+    b = _run(inp, 4)
+    for n in a:
+        assert orc.rel_err(b[n], a[n]) <= TOL_BF16, n
+
+
+def test_auto_plan_uses_segments_only_when_starved():
+    from palimpsa_b200.ops.palimpsa._core import plan_segments
+    assert plan_segments(8, 4096, 6, 128, 128) == 1       # 170M-shaped batch: the grid already fills the GPU
+    assert plan_segments(1, 131072, 12, 128, 128) == 4    # one long sequence: 96 CTAs -> 4 segments
+    assert plan_segments(1, 512, 2, 64, 64) == 1

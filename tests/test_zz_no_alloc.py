@@ -26,8 +26,8 @@ def _bwd_both(seed, B, T, H, K, V, dtype, unc):
     d = {n: x.to(DEV) for n, x in inp.items()}
     scale = K ** -0.5
     with torch.no_grad():
-        _, _, _, _, ckM, ckI, _ = _core.fwd_op(d["q"], d["k"], d["v"], d["b"], d["gt"], d["g"], d["Ip"], None, None,
-                                               None, scale, unc, True, False, False)
+        _, _, _, _, ckM, ckI, _, _ = _core.fwd_op(d["q"], d["k"], d["v"], d["b"], d["gt"], d["g"], d["Ip"], None, None,
+                                                  None, scale, unc, True, False, False, 1)
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     results = []
     for static in (False, True):
