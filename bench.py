@@ -136,6 +136,7 @@ def cpu_baseline(budget_s, cfg, steps=1, warmup=0):
     """Times the naive recurrence on a truncated sample (same B, H, d_k, d_v; T cut so that the whole
     call stays within ``budget_s`` seconds).  Returns (tokens/s, description, per-step seconds)."""
     B, H, K, V = cfg["B"], cfg["H"], cfg["K"], cfg["V"]
+    torch.set_num_threads(os.cpu_count() or 1)        # launchers pin OMP_NUM_THREADS=1; the baseline gets every core
     probe, _ = make_inputs(B, 4, H, K, V, torch.bfloat16, None, seed=1)
     cpu_step(probe)                                   # first call pays one-time costs
     t0 = time.perf_counter()

@@ -1,0 +1,241 @@
+"""Multi-GPU use of the Palimpsa operator: one process per GPU, ``torch.distributed`` for the plumbing.
+
+Two modes, neither of which exists in the reference (it has no collective at all; its multi-GPU runs
+come from the external trainer):
+
+* **batch x head sharding** -- the operator is independent per (sequence, head), so every rank simply
+  runs the single-GPU op on its slice (:func:`shard_batch`, :func:`shard_heads`).  No communication;
+  ``dg`` / ``dIp`` come out as per-rank partial sums, exactly like data-parallel parameter gradients.
+
+* **context parallelism** (:func:`cp_chunk_palimpsa`) -- one long sequence split contiguously over the
+  ranks of a group.  The recurrence is linear in the state pair (M, J = I - Ip) with a scalar decay per
+  head, so every rank first summarises its own tokens (end state from a zero start + total decay)
+  without waiting for anybody; the true boundary states then travel down the ranks as ONE small
+  point-to-point message per hop (2 x N x H x V x KP floats: 1.5 MB at H=12, d=128), and all ranks run
+  their heavy pass side by side.  Backward mirrors this with the state gradients travelling up.
+
+The hop logic is written against a small backend interface so that the protocol can be exercised with
+CPU ranks (gloo) and a float64 stand-in for the kernels; the product backend below drives the CUDA
+library through its C ABI.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _lib as L
+
+
+# --------------------------------------------------------------------------------------------------
+# batch x head sharding (no communication)
+# --------------------------------------------------------------------------------------------------
+def shard_bounds(n: int, rank: int, world: int):
+    """Contiguous, balanced split of ``n`` units: the first ``n % world`` ranks get one extra."""
+    base, extra = divmod(n, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def shard_batch(x: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    lo, hi = shard_bounds(x.shape[0], rank, world)
+    return x[lo:hi]
+
+
+def shard_heads(x: torch.Tensor, rank: int, world: int, head_dim: int = 2) -> torch.Tensor:
+    """Slice of the head axis (dim 2 of ``[B,T,H,*]`` tensors, dim 0 of ``g`` / ``Ip``)."""
+    lo, hi = shard_bounds(x.shape[head_dim], rank, world)
+    return x.narrow(head_dim, lo, hi - lo)
+
+
+# --------------------------------------------------------------------------------------------------
+# boundary-state hops
+# --------------------------------------------------------------------------------------------------
+def _peer(group, r: int) -> int:
+    return r if group is None else dist.get_global_rank(group, r)
+
+
+def chain_down(rank: int, world: int, group, local: Callable[[Optional[torch.Tensor]], torch.Tensor],
+               like: torch.Tensor) -> None:
+    """Forward hop: rank r receives the boundary state from rank r-1 (rank 0 gets ``None``), runs
+    ``local(state)`` which must return the state after its own tokens, and sends that to rank r+1.
+    A peer that died or raised before sending surfaces here as the process group's timeout error."""
+    inc = None
+    if rank > 0:
+        inc = torch.empty_like(like)
+        dist.recv(inc, src=_peer(group, rank - 1), group=group)
+    out = local(inc)
+    if rank < world - 1:
+        dist.send(out.contiguous(), dst=_peer(group, rank + 1), group=group)
+
+
+def chain_up(rank: int, world: int, group, local: Callable[[Optional[torch.Tensor]], torch.Tensor],
+             like: torch.Tensor) -> None:
+    """Backward hop: the mirror image, state gradients travel from rank r+1 to rank r."""
+    inc = None
+    if rank < world - 1:
+        inc = torch.empty_like(like)
+        dist.recv(inc, src=_peer(group, rank + 1), group=group)
+    out = local(inc)
+    if rank > 0:
+        dist.send(out.contiguous(), dst=_peer(group, rank - 1), group=group)
+
+
+# --------------------------------------------------------------------------------------------------
+# CUDA backend of the context-parallel op
+# --------------------------------------------------------------------------------------------------
+class _CudaLocal:
+    """One rank's share of the sequence, driven through the C ABI (segment entry points)."""
+
+    def __init__(self, q, k, v, b, gt, g, Ip, scale, num_segments, first_rank: bool):
+        from .ops.palimpsa import _core
+        self.core = _core
+        self.lib = L.lib()
+        self.t = (q, k, v, b, gt, g, Ip)
+        self.N, self.T, self.H, self.K = q.shape
+        self.V = v.shape[-1]
+        self.KP = _core.padded_k(self.K)
+        self.scale = float(scale)
+        self.G = max(1, int(num_segments))
+        self.seg_len = _core.segment_len(max(self.T, 1), self.G)
+        self.first = first_rank
+        self.dev = q.device
+        self.stream = _core._stream(q)
+        self.sg, self.bufs = _core.make_segments(self.N, self.G, self.seg_len, self.H, self.V, self.K, self.dev, True)
+        self.prob = _core._problem(q, k, v, b, gt, g, Ip, None, None, None, None, self.scale, 0)
+
+    def state_like(self):
+        return torch.empty(2, self.N, self.H, self.V, self.KP, dtype=torch.float32, device=self.dev)
+
+    def summary(self):
+        L.check(self.lib.palimpsa_segment_summary(C.byref(self.prob), C.byref(self.sg), self.stream), "segment summary")
+
+    def combine(self, inc):
+        out = self.state_like()
+        a, bb = (None, None) if inc is None else (inc[0].data_ptr(), inc[1].data_ptr())
+        L.check(self.lib.palimpsa_cp_combine(C.byref(self.prob), C.byref(self.sg), a, bb, out[0].data_ptr(),
+                                             out[1].data_ptr(), self.stream), "boundary scan")
+        return out
+
+    def forward(self, save_ckpt: bool):
+        q, k, v, b, gt, g, Ip = self.t
+        core = self.core
+        o = torch.empty(self.N, self.T, self.H, self.V, dtype=q.dtype, device=self.dev)
+        fmu = torch.empty(self.N, self.H, self.V, self.K, dtype=torch.float32, device=self.dev)
+        fI = torch.empty_like(fmu)
+        ckM = ckI = None
+        if save_ckpt:
+            slots = core._ckpt_slots(self.N * self.T, self.N)
+            ckM = torch.empty(slots, self.H, self.V, self.KP, dtype=torch.float32, device=self.dev)
+            ckI = torch.empty_like(ckM)
+        prm = L.FwdParams()
+        prm.struct_size = C.sizeof(L.FwdParams)
+        prm.p = self.prob
+        prm.o = core._ptr(o)
+        prm.final_mu, prm.final_I = fmu.data_ptr(), fI.data_ptr()
+        prm.ckpt_M, prm.ckpt_I = core._ptr(ckM), core._ptr(ckI)
+        L.check(self.lib.palimpsa_chunk_fwd_segments(C.byref(prm), C.byref(self.sg), self.stream), "forward (segments)")
+        return o, fmu, fI, ckM, ckI
+
+    # ---- backward ----
+    def _bwd_params(self, do, ckM, ckI, outs=None, ws=None):
+        core = self.core
+        prm = L.BwdParams()
+        prm.struct_size = C.sizeof(L.BwdParams)
+        prm.p = self.prob
+        if not self.first:
+            prm.p.flags |= L.FLAG_EXPLICIT_INIT      # this rank starts from a received state, not from the prior
+        prm.d_o = core._ptr(do)
+        prm.ckpt_M, prm.ckpt_I = ckM.data_ptr(), ckI.data_ptr()
+        if outs is not None:
+            prm.dq, prm.dk, prm.dv, prm.db, prm.dgt, prm.dg, prm.dIp = [core._ptr(x) for x in outs]
+            prm.workspace, prm.workspace_bytes = ws.data_ptr(), ws.numel()
+        return prm
+
+    def bwd_segments(self, decay):
+        sg, bufs = self.core.make_segments(self.N, self.G, self.seg_len, self.H, self.V, self.K, self.dev, False)
+        sg.decay = decay.data_ptr()
+        return sg, bufs
+
+    def bwd_carry(self, do, ckM, ckI, sg):
+        prm = self._bwd_params(do, ckM, ckI)
+        L.check(self.lib.palimpsa_chunk_bwd_segments(C.byref(prm), C.byref(sg), 1, self.stream), "backward carry pass")
+
+    def combine_bwd(self, sg, inc):
+        out = self.state_like()
+        a, bb = (None, None) if inc is None else (inc[0].data_ptr(), inc[1].data_ptr())
+        L.check(self.lib.palimpsa_cp_combine_bwd(C.byref(self.prob), C.byref(sg), a, bb, out[0].data_ptr(),
+                                                 out[1].data_ptr(), self.stream), "boundary scan (backward)")
+        return out
+
+    def backward(self, do, ckM, ckI, sg):
+        q, k, v, b, gt, g, Ip = self.t
+        outs = [torch.empty_like(q), torch.empty_like(k), torch.empty_like(v), torch.empty_like(b),
+                torch.empty(self.N, self.T, self.H, dtype=torch.float32, device=self.dev),
+                torch.empty(self.H, dtype=torch.float32, device=self.dev),
+                torch.empty(self.H, dtype=torch.float32, device=self.dev)]
+        prm = self._bwd_params(do, ckM, ckI)
+        need = self.lib.palimpsa_bwd_workspace_bytes(C.byref(prm.p))
+        ws = torch.empty(max(need, 256), dtype=torch.uint8, device=self.dev)
+        prm = self._bwd_params(do, ckM, ckI, outs, ws)
+        sg.rloc_M = sg.rloc_I = None
+        L.check(self.lib.palimpsa_chunk_bwd_segments(C.byref(prm), C.byref(sg), 0, self.stream), "backward (segments)")
+        return outs
+
+
+class _CpChunkPalimpsa(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, b, gt, g, Ip, scale, group, num_segments, reduce_param_grads):
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        loc = _CudaLocal(q, k, v, b, gt, g, Ip, scale, num_segments, first_rank=(rank == 0))
+        need_grad = any(ctx.needs_input_grad[:7])
+        with torch.cuda.device(q.device):
+            loc.summary()                                    # no dependence on other ranks
+            chain_down(rank, world, group, loc.combine, loc.state_like())
+            o, fmu, fI, ckM, ckI = loc.forward(save_ckpt=need_grad)
+        ctx.loc, ctx.group, ctx.reduce = loc, group, reduce_param_grads
+        ctx.rank, ctx.world = rank, world
+        if need_grad:
+            ctx.save_for_backward(ckM, ckI, loc.bufs["decay"])
+        ctx.mark_non_differentiable(fmu, fI)
+        return o, fmu, fI
+
+    @staticmethod
+    def backward(ctx, do, _dmu, _dI):
+        loc = ctx.loc
+        ckM, ckI, decay = ctx.saved_tensors
+        do = do.to(loc.t[0].dtype).contiguous()
+        with torch.cuda.device(do.device):
+            sg, bufs = loc.bwd_segments(decay)
+            loc.bwd_carry(do, ckM, ckI, sg)                  # zero-carry state gradients of every segment
+            chain_up(ctx.rank, ctx.world, ctx.group, lambda inc: loc.combine_bwd(sg, inc), loc.state_like())
+            dq, dk, dv, db, dgt, dg, dIp = loc.backward(do, ckM, ckI, sg)
+            if ctx.reduce and ctx.world > 1:
+                pg = torch.stack([dg, dIp])
+                dist.all_reduce(pg, group=ctx.group)
+                dg, dIp = pg[0], pg[1]
+        return dq, dk, dv, db, dgt, dg, dIp, None, None, None, None
+
+
+def cp_chunk_palimpsa(q, k, v, b, gt, g, Ip, group=None, scale=None, output_final_state=False, num_segments=None,
+                      reduce_param_grads=True):
+    """Context-parallel ``chunk_palimpsa``: every rank of ``group`` passes ITS contiguous share of the
+    sequence (``q,k [B,T_local,H,K]`` ...; shares in rank order; lengths may differ) and gets its share of
+    ``o`` and of the gradients.  With ``output_final_state`` also returns the state after this rank's
+    last token (the sequence's final state on the last rank).  ``dg`` / ``dIp`` are summed over the group
+    unless ``reduce_param_grads=False``.  The sequence starts from the prior (no explicit initial state)."""
+    from .ops.palimpsa import _core
+    _core._require_cuda(q, k, v, b, gt, g, Ip)
+    if scale is None:
+        scale = q.shape[-1] ** -0.5
+    io = q.dtype
+    q, k, v, b = [x.to(io).contiguous() for x in (q, k, v, b)]
+    gt, g, Ip = [x.float().contiguous() for x in (gt, g, Ip)]
+    B, T, H, K = q.shape
+    if num_segments is None:
+        num_segments = _core.plan_segments(B, T, H, K, v.shape[-1])
+    o, fmu, fI = _CpChunkPalimpsa.apply(q, k, v, b, gt, g, Ip, float(scale), group, int(num_segments),
+                                        bool(reduce_param_grads))
+    return (o, fmu, fI) if output_final_state else o

@@ -1,0 +1,81 @@
+"""Context parallelism on real GPUs (needs >= 2): every rank holds a contiguous share of one sequence;
+outputs and gradients must equal the single-GPU op on the whole sequence.  Ranks are child processes,
+one per GPU, NCCL point-to-point for the boundary states (NVLS off: a plain send/recv needs none)."""
+import os
+import socket
+import sys
+import traceback
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q_out, dtype_name, T, G):
+    try:
+        sys.path.insert(0, ROOT)
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        import datetime
+        import torch.distributed as dist
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120),
+                                device_id=torch.device("cuda", rank))
+        from oracle import palimpsa_oracle as orc
+        from palimpsa_b200.ops import chunk_palimpsa
+        from palimpsa_b200.parallel import cp_chunk_palimpsa, shard_bounds
+        dtype = getattr(torch, dtype_name)
+        dev = torch.device("cuda", rank)
+        inp = orc.make_inputs(5, B=2, T=T, H=3, K=64, V=48, dtype=dtype)
+        inp["gt"] = inp["gt"] * 0.05
+        names = ("q", "k", "v", "b", "gt", "g", "Ip")
+        full = {n: inp[n].to(dev).requires_grad_(True) for n in names}
+        o_ref, mu_ref, I_ref = chunk_palimpsa(*[full[n] for n in names], output_final_state=True)
+        o_ref.backward(inp["do"].to(dev))
+        lo, hi = shard_bounds(T, rank, world)
+        loc = {n: (inp[n][:, lo:hi] if inp[n].dim() >= 3 else inp[n]).to(dev).contiguous().requires_grad_(True)
+               for n in names}
+        o, mu, I = cp_chunk_palimpsa(*[loc[n] for n in names], output_final_state=True, num_segments=G)
+        o.backward(inp["do"][:, lo:hi].to(dev))
+        torch.cuda.synchronize()
+        tol = 1e-5 if dtype == torch.float32 else 2e-2
+        errs = {"o": orc.rel_err(o, o_ref[:, lo:hi])}
+        for n in ("q", "k", "v", "b", "gt"):
+            errs["d" + n] = orc.rel_err(loc[n].grad, full[n].grad[:, lo:hi])
+        for n in ("g", "Ip"):
+            errs["d" + n] = orc.rel_err(loc[n].grad, full[n].grad)
+        if rank == world - 1:
+            errs["final_mu"] = orc.rel_err(mu, mu_ref)
+            errs["final_I"] = orc.rel_err(I, I_ref)
+        bad = {n: e for n, e in errs.items() if not e <= 2 * tol}
+        q_out.put((rank, "ok" if not bad else "bad", errs))
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        q_out.put((rank, "error", traceback.format_exc()))
+
+
+@pytest.mark.parametrize("dtype_name,T,G", [("float32", 300, 1), ("float32", 333, 3), ("bfloat16", 1024, 2)])
+def test_cp_matches_single_gpu(dtype_name, T, G):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q_out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q_out, dtype_name, T, G)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q_out.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(60)
+    for g in got:
+        assert g[1] == "ok", g
