@@ -295,14 +295,12 @@ def run_ours(args, rank, world, local_rank):
     names_in = ("q", "k", "v", "b", "gt", "g", "Ip", "do")
     out_host = {}
 
+    from palimpsa_b200.host_pipeline import HostPipeline
+    slices = int(os.environ.get("PALIMPSA_E2E_SLICES", "4"))
+    pipe = HostPipeline(host, dev, slices=slices)
+
     def e2e_step():
-        dd = {n: host[n].to(dev, non_blocking=True) for n in names_in}
-        o, grads = fwd_bwd(dd)
-        for n, x in zip(("o", "dq", "dk", "dv", "db", "dgt", "dg", "dIp"), [o] + grads):
-            if n not in out_host:
-                out_host[n] = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
-            out_host[n].copy_(x, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        out_host.update(pipe.run(host))
 
     e2e_steps = max(3, min(args.steps, 10))
     ms_e2e = time_region(e2e_step, e2e_steps, 3, world, dev)
@@ -330,8 +328,9 @@ def run_ours(args, rank, world, local_rank):
                        "sharding": "batch x head across GPUs, no collective",
                        "l2": f"inputs per step {in_bytes / 2 ** 20:.0f} MiB > L2 {L2_BYTES // 2 ** 20} MiB (no flush needed)"},
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": ms_e2e / e2e_steps},
-            "gpu_launches": 4 * args.steps, "clocks": clocks, "roofline": roof,
+                    "ms_per_step": ms_e2e / e2e_steps, "api": "palimpsa_b200.host_pipeline.HostPipeline.run",
+                    "batch_slices": slices},
+            "gpu_launches": 4 * args.steps + 4 * slices * (e2e_steps + 3), "clocks": clocks, "roofline": roof,
             "cpu_baseline": {"value": cb_val, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
                              "sample": cb_sample}}
     print(json.dumps(line), flush=True)

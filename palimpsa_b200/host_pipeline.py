@@ -1,0 +1,102 @@
+"""Forward + backward of ``chunk_palimpsa`` for data that lives in HOST memory.
+
+The op is independent per sequence, so a batch held in pinned host buffers can be processed in slices:
+while slice i computes, slice i+1 is on its way to the device and the results of slice i-1 are on their
+way back (three CUDA streams; PCIe is full duplex).  Device staging buffers are allocated once and
+reused, so that a step makes no allocator round trip on the copy streams.  ``dg`` / ``dIp`` (sums over
+the batch) are accumulated on the device and returned once.  Not part of the reference, whose ops only
+see device tensors; it exists because end-to-end throughput from host buffers is copy-bound otherwise.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .ops import chunk_palimpsa
+
+_IN_BATCHED = ("q", "k", "v", "b", "gt", "do")
+_OUT_BATCHED = ("o", "dq", "dk", "dv", "db", "dgt")
+
+
+class HostPipeline:
+    """Reusable pipeline for one problem shape.  ``run(host)`` takes pinned CPU tensors ``q,k,v,b,do``
+    ``[B,T,H,*]``, ``gt [B,T,H]``, ``g,Ip [H]`` and returns pinned CPU tensors ``o, dq, dk, dv, db, dgt,
+    dg, dIp``; it returns after everything has landed on the host."""
+
+    def __init__(self, host: Dict[str, torch.Tensor], device, slices: int = 4):
+        self.dev = torch.device(device)
+        B = host["q"].shape[0]
+        self.slices = max(1, min(slices, B))
+        self.bounds = [(i * B // self.slices, (i + 1) * B // self.slices) for i in range(self.slices)]
+        width = max(hi - lo for lo, hi in self.bounds)
+        # two staging slots: slice i+1 uploads while slice i computes
+        self.slots = [{n: torch.empty((width,) + tuple(host[n].shape[1:]), dtype=host[n].dtype, device=self.dev)
+                       for n in _IN_BATCHED} for _ in range(2)]
+        self.out = {}
+        self.s_in, self.s_out = torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev)
+        self.free = [None, None]   # event after which a slot may be overwritten
+
+    def run(self, host: Dict[str, torch.Tensor], scale=None) -> Dict[str, torch.Tensor]:
+        dev, cur = self.dev, torch.cuda.current_stream(self.dev)
+        s_in, s_out = self.s_in, self.s_out
+        B = host["q"].shape[0]
+        s_in.wait_stream(cur)
+        with torch.cuda.stream(s_in):
+            g = host["g"].to(dev, non_blocking=True)
+            Ip = host["Ip"].to(dev, non_blocking=True)
+        g.record_stream(cur)
+        Ip.record_stream(cur)
+
+        def upload(i):
+            lo, hi = self.bounds[i]
+            slot = self.slots[i % 2]
+            with torch.cuda.stream(s_in):
+                if self.free[i % 2] is not None:
+                    s_in.wait_event(self.free[i % 2])
+                for n in _IN_BATCHED:
+                    slot[n][: hi - lo].copy_(host[n][lo:hi], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(s_in)
+            return ev
+
+        ready = {0: upload(0)}
+        dg_acc = dIp_acc = None
+        pending = []
+        for i, (lo, hi) in enumerate(self.bounds):
+            if i + 1 < self.slices:
+                ready[i + 1] = upload(i + 1)
+            cur.wait_event(ready.pop(i))
+            slot = self.slots[i % 2]
+            leaves = [slot[n][: hi - lo].detach().requires_grad_(True) for n in ("q", "k", "v", "b", "gt")]
+            gl, ipl = g.detach().requires_grad_(True), Ip.detach().requires_grad_(True)
+            o = chunk_palimpsa(*leaves, gl, ipl, scale=scale)
+            o.backward(slot["do"][: hi - lo])
+            res = dict(zip(_OUT_BATCHED, [o.detach()] + [x.grad for x in leaves]))
+            dg_acc = gl.grad if dg_acc is None else dg_acc + gl.grad
+            dIp_acc = ipl.grad if dIp_acc is None else dIp_acc + ipl.grad
+            done = torch.cuda.Event()
+            done.record(cur)
+            self.free[i % 2] = done
+            s_out.wait_event(done)
+            with torch.cuda.stream(s_out):
+                for n, x in res.items():
+                    if n not in self.out:
+                        self.out[n] = torch.empty((B,) + tuple(x.shape[1:]), dtype=x.dtype, pin_memory=True)
+                    self.out[n][lo:hi].copy_(x, non_blocking=True)
+            pending.append(res)          # keep the device results alive until their copies are done
+        for n, x in (("dg", dg_acc), ("dIp", dIp_acc)):
+            if n not in self.out:
+                self.out[n] = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
+            self.out[n].copy_(x, non_blocking=True)
+        cur.synchronize()
+        s_out.synchronize()
+        pending.clear()
+        return self.out
+
+
+def fwd_bwd_from_host(host: Dict[str, torch.Tensor], device, slices: int = 4, scale=None,
+                      pipeline: Optional[HostPipeline] = None) -> Dict[str, torch.Tensor]:
+    """One-shot convenience wrapper; pass ``pipeline`` to reuse staging buffers across calls."""
+    pipe = pipeline or HostPipeline(host, device, slices)
+    return pipe.run(host, scale=scale)
