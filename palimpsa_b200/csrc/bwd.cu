@@ -81,7 +81,7 @@ __host__ __device__ inline BwdSmem bwd_smem_layout(int KP, int TV, int NE, int n
     s.slots = take(2 * 2 * NE * nthr * 4);
     s.ck_stage = 2 * TV * KP * 4;
     s.ckb = take(2 * s.ck_stage);
-    s.kred = take(GR * WV * 2 * KP * 4);
+    s.kred = take(2 * GR * WV * 2 * KP * 4);  // two group buffers: one barrier per group
     s.raw = off;
     int r = 0;
     auto rtake = [&](int bytes) {
@@ -345,19 +345,44 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
             for (int q = 0; q < NP; ++q)
                 sl[(r * NP + q) * NTHR] = make_float4(s.M[r][q].x, s.M[r][q].y, s.I[r][q].x, s.I[r][q].y);
     };
+    // operand loads: two adjacent 8-byte pairs come in as one 16-byte load where the tiling allows it
+    auto ld_cols = [&](const float2* base, int tl, float2 (&dst)[NP]) {
+        if constexpr (NP % 2 == 0) {
+#pragma unroll
+            for (int q = 0; q < NP; q += 2) {
+                const float4 x = *reinterpret_cast<const float4*>(base + tl * KP2 + q);
+                dst[q] = make_float2(x.x, x.y);
+                dst[q + 1] = make_float2(x.z, x.w);
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < NP; ++q) dst[q] = base[tl * KP2 + q];
+        }
+    };
+    auto ld_rows = [&](const float2* base, int tl, float2 (&dst)[RV]) {
+        if constexpr (RV % 2 == 0) {
+#pragma unroll
+            for (int r = 0; r < RV; r += 2) {
+                const float4 x = *reinterpret_cast<const float4*>(base + tl * TV + r);
+                dst[r] = make_float2(x.x, x.y);
+                dst[r + 1] = make_float2(x.z, x.w);
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < RV; ++r) dst[r] = base[tl * TV + r];
+        }
+    };
     // one forward step of the recurrence on token tl of the staged block
     auto fstep = [&](State<RV, NP>& s, int tl) {
         const float4 fv = fc2[tl];
         const float2 ff = make_float2(fv.x, fv.y), cc = make_float2(fv.z, fv.w);
-        float2 vr[RV], br[RV];
-#pragma unroll
-        for (int r = 0; r < RV; ++r) {
-            vr[r] = vs2[tl * TV + r];
-            br[r] = bs2[tl * TV + r];
-        }
+        float2 vr[RV], br[RV], kpv[NP];
+        ld_rows(vs2, tl, vr);
+        ld_rows(bs2, tl, br);
+        ld_cols(ks2, tl, kpv);
 #pragma unroll
         for (int q = 0; q < NP; ++q) {
-            const float2 kp = ks2[tl * KP2 + q];
+            const float2 kp = kpv[q];
             const float2 kk = fmul2(kp, kp);
 #pragma unroll
             for (int r = 0; r < RV; ++r) {
@@ -441,23 +466,33 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                 const int tl = gi * GR + j;
                 const float2 fn = fn2[tl];
                 float2 dqs[NP], Ak[NP], Bk[NP], Uk[NP];
-                float2 Sa = make_float2(0.f, 0.f), Sb = Sa, Sc = Sa;
+                float2 Sa[RV], Sb[RV], Sc[RV];  // one accumulator per row: shorter dependent chains
+#pragma unroll
+                for (int r = 0; r < RV; ++r) Sa[r] = Sb[r] = Sc[r] = make_float2(0.f, 0.f);
 #pragma unroll
                 for (int q = 0; q < NP; ++q) dqs[q] = Ak[q] = Bk[q] = Uk[q] = make_float2(0.f, 0.f);
                 float2 kp[NP], kk[NP], qp[NP], qq[NP];
+                ld_cols(ks2, tl, kp);
+                ld_cols(qs2, tl, qp);
 #pragma unroll
                 for (int q = 0; q < NP; ++q) {
-                    kp[q] = ks2[tl * KP2 + q];
                     kk[q] = fmul2(kp[q], kp[q]);
-                    qp[q] = qs2[tl * KP2 + q];
-                    qq[q] = UNC ? qqs2[tl * KP2 + q] : make_float2(0.f, 0.f);
+                    qq[q] = make_float2(0.f, 0.f);
                 }
+                if (UNC) ld_cols(qqs2, tl, qq);
+                float2 vvr[RV], bvr[RV], dyr[RV], dyvr[RV];
+                ld_rows(vs2, tl, vvr);
+                ld_rows(bs2, tl, bvr);
+                ld_rows(dys2, tl, dyr);
+#pragma unroll
+                for (int r = 0; r < RV; ++r) dyvr[r] = make_float2(0.f, 0.f);
+                if (UNC) ld_rows(dyvs2, tl, dyvr);
 #pragma unroll
                 for (int r = 0; r < RV; ++r) {
-                    const float2 vv = vs2[tl * TV + r];
-                    const float2 bv = bs2[tl * TV + r];
-                    const float2 dy = dys2[tl * TV + r];
-                    const float2 dyv = UNC ? dyvs2[tl * TV + r] : make_float2(0.f, 0.f);
+                    const float2 vv = vvr[r];
+                    const float2 bv = bvr[r];
+                    const float2 dy = dyr[r];
+                    const float2 dyv = dyvr[r];
                     float2 dva = make_float2(0.f, 0.f), dba = dva;
 #pragma unroll
                     for (int q = 0; q < NP; ++q) {
@@ -476,9 +511,9 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                             Bk[q] = ffma2(nGI[r][q], bv, Bk[q]);
                             dva = ffma2(GM[r][q], kp[q], dva);
                             dba = ffma2(nGI[r][q], kk[q], dba);
-                            Sa = ffma2(GM[r][q], P[j].M[r][q], Sa);
-                            Sb = ffma2(nGI[r][q], P[j].I[r][q], Sb);
-                            Sc = fadd2(Sc, nGI[r][q]);
+                            Sa[r] = ffma2(GM[r][q], P[j].M[r][q], Sa[r]);
+                            Sb[r] = ffma2(nGI[r][q], P[j].I[r][q], Sb[r]);
+                            Sc[r] = fadd2(Sc[r], nGI[r][q]);
                         }
                     }
                     red1[(j * RV + r) * 2 + 0] = dva.x + dva.y;
@@ -486,7 +521,7 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                 }
                 // this row group's share of dq and dk for the token -> shared memory
                 if (!CO) {
-                    float2* dst = kred2 + ((j * WV + wv) * 2) * KP2 + NP * kg;
+                    float2* dst = kred2 + (gi & 1) * (GR * WV * 2 * KP2) + ((j * WV + wv) * 2) * KP2 + NP * kg;
                     const float2 sc2 = dup2(p.scale), m2 = dup2(-2.f);
 #pragma unroll
                     for (int q = 0; q < NP; ++q) {
@@ -496,8 +531,15 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                         dst[KP2 + q] = ffma2(fmul2(m2, kp[q]), Bk[q], Ak[q]);
                     }
                 }
-                const float sc_ = Sc.x + Sc.y;
-                red2[j * 2 + 0] = (Sa.x + Sa.y) - (Sb.x + Sb.y) + iph * sc_;
+                float2 sa = Sa[0], sb = Sb[0], scv = Sc[0];
+#pragma unroll
+                for (int r = 1; r < RV; ++r) {
+                    sa = fadd2(sa, Sa[r]);
+                    sb = fadd2(sb, Sb[r]);
+                    scv = fadd2(scv, Sc[r]);
+                }
+                const float sc_ = scv.x + scv.y;
+                red2[j * 2 + 0] = (sa.x + sa.y) - (sb.x + sb.y) + iph * sc_;
                 red2[j * 2 + 1] = -sc_;
             }
             if (CO) continue;  // carry-only pass: nothing but the state gradients is wanted
@@ -526,7 +568,7 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
             const int ng = min(GR, nt - gi * GR);  // tokens of the group that exist (<= 0 past the sequence end)
             for (int i = tid; i < ng * KP2; i += NTHR) {
                 const int j = i / KP2, pi = i - j * KP2;
-                const float2* src = kred2 + (j * WV * 2) * KP2 + pi;
+                const float2* src = kred2 + (gi & 1) * (GR * WV * 2 * KP2) + (j * WV * 2) * KP2 + pi;
                 float2 s0 = make_float2(0.f, 0.f), s1 = s0;
 #pragma unroll
                 for (int x = 0; x < WV; ++x) {
@@ -537,8 +579,10 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                 reinterpret_cast<float2*>(a.dq_part)[e] = s0;
                 reinterpret_cast<float2*>(a.dk_part)[e] = s1;
             }
-            __syncthreads();
+            // no second barrier: the next group writes the other kred buffer, and the barrier after ITS
+            // reverse walk orders this group's reads before the group after that reuses this buffer
         }
+        if (!CO) __syncthreads();  // dvs / dbs / wred of the whole block are complete
 
         // ---- block epilogue: dv, db rows and the per-token scalars -----------------------------------
         if (CO) continue;
