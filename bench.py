@@ -343,12 +343,24 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--profile-batch", type=int, default=4, help="batch size of --profile-case")
+    ap.add_argument("--profile-segments", type=int, default=1,
+                    help="with --profile-case: run one 32768-token sequence (H=12) cut into this many segments")
     ap.add_argument("--profile-case", action="store_true",
                     help="run a few forward+backward steps of a half-size batch (B=4) and exit: the small case "
                          "that profiler captures are taken on")
     args = ap.parse_args()
     if args.profile_case:
         dev = torch.device("cuda", 0)
+        if args.profile_segments > 1:
+            # one long sequence cut into segments: exercises the summary (tensor-core) and scan kernels
+            from palimpsa_b200.ops import chunk_palimpsa
+            _, d = make_inputs(1, 32768, 12, C2["K"], C2["V"], torch.bfloat16, dev)
+            for _ in range(3):
+                leaves = [d[n].detach().requires_grad_(True) for n in ("q", "k", "v", "b", "gt", "g", "Ip")]
+                chunk_palimpsa(*leaves, num_segments=args.profile_segments).backward(d["do"])
+            torch.cuda.synchronize()
+            print("profile case (segments) done")
+            return
         _, d = make_inputs(args.profile_batch, C2["T"], C2["H"], C2["K"], C2["V"], torch.bfloat16, dev)
         for _ in range(3):
             fwd_bwd(d)

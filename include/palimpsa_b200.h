@@ -135,6 +135,10 @@ typedef struct palimpsa_segments {
 /* Fills sum_M, sum_J and decay for every segment (no reciprocal, no output: the cheap pass). */
 int palimpsa_segment_summary(const palimpsa_problem *p, const palimpsa_segments *segs, void *cuda_stream);
 
+/* Diagnostic: 0 unless a bounded wait inside the tensor-core summary kernel (bf16 inputs: tcgen05 MMAs
+ * into TMEM) ever gave up on this device; then the code of the wait.  Synchronises the device. */
+int palimpsa_tensor_core_status(void);
+
 /* Forward boundary scan: start_M/start_I of every segment from the summaries.  The state before
  * segment 0 is (in_M, in_J) [N,H,V,KP] in (M, J) form if given (a previous rank's end state), else
  * p->init_mu/init_I, else the prior (0, 0).  If out_M/out_J are given they receive the state after

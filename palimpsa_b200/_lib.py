@@ -65,6 +65,7 @@ SYMBOLS = {
     "palimpsa_padded_k": (C.c_int, [C.c_int]),
     "palimpsa_ckpt_slots": (C.c_longlong, [C.POINTER(Problem)]),
     "palimpsa_segment_summary": (C.c_int, [C.POINTER(Problem), C.POINTER(Segments), C.c_void_p]),
+    "palimpsa_tensor_core_status": (C.c_int, []),
     "palimpsa_cp_combine": (C.c_int, [C.POINTER(Problem), C.POINTER(Segments), C.c_void_p, C.c_void_p, C.c_void_p,
                                       C.c_void_p, C.c_void_p]),
     "palimpsa_cp_combine_bwd": (C.c_int, [C.POINTER(Problem), C.POINTER(Segments), C.c_void_p, C.c_void_p, C.c_void_p,

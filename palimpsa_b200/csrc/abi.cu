@@ -1,5 +1,7 @@
 // extern "C" surface of libpalimpsa_b200.so: argument validation and dispatch.  No kernel lives
 // here; see fwd.cu and bwd.cu.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "host.h"
 
@@ -138,11 +140,15 @@ int palimpsa_segment_summary(const palimpsa_problem* p, const palimpsa_segments*
     rc = check_segments(*p, sg);
     if (rc) return rc;
     if (!sg->sum_M || !sg->sum_J || !sg->decay) return PALIMPSA_E_NULL;
+    static const bool force_simt = getenv("PALIMPSA_SUMMARY_SIMT") != nullptr;  // development switch
+    if (!force_simt && summary_tc_supported(*p)) return launch_summary_tc(*p, *sg, static_cast<cudaStream_t>(cuda_stream));
     palimpsa_fwd_params prm{};
     prm.struct_size = sizeof(prm);
     prm.p = *p;
     return launch_fwd(&prm, sg, true, static_cast<cudaStream_t>(cuda_stream));
 }
+
+int palimpsa_tensor_core_status(void) { return summary_tc_status(); }
 
 int palimpsa_cp_combine(const palimpsa_problem* p, const palimpsa_segments* sg, const float* in_M, const float* in_J,
                         float* out_M, float* out_J, void* cuda_stream) {

@@ -81,7 +81,7 @@ __host__ __device__ inline BwdSmem bwd_smem_layout(int KP, int TV, int NE, int n
     s.slots = take(2 * 2 * NE * nthr * 4);
     s.ck_stage = 2 * TV * KP * 4;
     s.ckb = take(2 * s.ck_stage);
-    s.kred = take(2 * GR * WV * 2 * KP * 4);  // two group buffers: one barrier per group
+    s.kred = take((nthr > 256 ? 1 : 2) * GR * WV * 2 * KP * 4);  // two group buffers (one barrier per group) if they fit
     s.raw = off;
     int r = 0;
     auto rtake = [&](int bytes) {
@@ -237,6 +237,7 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
     constexpr int KP = RK * KG, VG = 32 / KG, NP = RK / 2, NE = RV * RK, KP2 = KP / 2;
     constexpr int TV = W * VG * RV, WV = W * VG, NTHR = 32 * W;
     constexpr int NG = TB / GR;       // groups per block
+    constexpr int KBUF = NTHR > 256 ? 1 : 2;  // shared-memory buffers for the d_k-indexed partials
     constexpr int NR1 = GR * RV * 2;  // per-group d_v-indexed partials of a thread: (token, row, dv|db)
     constexpr int NR2 = GR * 2;       // per-group per-token scalars: (token, df|sum GI)
     extern __shared__ __align__(16) unsigned char sm[];
@@ -521,7 +522,7 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                 }
                 // this row group's share of dq and dk for the token -> shared memory
                 if (!CO) {
-                    float2* dst = kred2 + (gi & 1) * (GR * WV * 2 * KP2) + ((j * WV + wv) * 2) * KP2 + NP * kg;
+                    float2* dst = kred2 + (gi & (KBUF - 1)) * (GR * WV * 2 * KP2) + ((j * WV + wv) * 2) * KP2 + NP * kg;
                     const float2 sc2 = dup2(p.scale), m2 = dup2(-2.f);
 #pragma unroll
                     for (int q = 0; q < NP; ++q) {
@@ -568,7 +569,7 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
             const int ng = min(GR, nt - gi * GR);  // tokens of the group that exist (<= 0 past the sequence end)
             for (int i = tid; i < ng * KP2; i += NTHR) {
                 const int j = i / KP2, pi = i - j * KP2;
-                const float2* src = kred2 + (gi & 1) * (GR * WV * 2 * KP2) + (j * WV * 2) * KP2 + pi;
+                const float2* src = kred2 + (gi & (KBUF - 1)) * (GR * WV * 2 * KP2) + (j * WV * 2) * KP2 + pi;
                 float2 s0 = make_float2(0.f, 0.f), s1 = s0;
 #pragma unroll
                 for (int x = 0; x < WV; ++x) {
@@ -579,8 +580,9 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                 reinterpret_cast<float2*>(a.dq_part)[e] = s0;
                 reinterpret_cast<float2*>(a.dk_part)[e] = s1;
             }
-            // no second barrier: the next group writes the other kred buffer, and the barrier after ITS
-            // reverse walk orders this group's reads before the group after that reuses this buffer
+            // with two buffers no second barrier is needed: the next group writes the other buffer, and the
+            // barrier after ITS reverse walk orders this group's reads before the buffer is reused
+            if (KBUF == 1) __syncthreads();
         }
         if (!CO) __syncthreads();  // dvs / dbs / wred of the whole block are complete
 
@@ -730,11 +732,13 @@ static BwdConfig bwd_config(const palimpsa_problem& p) {
     int W = (rpw == 1 || p.V > 4 * rpw) ? 8 : 4;
     static const int force_w = [] { const char* e = getenv("PALIMPSA_BWD_WARPS"); return e ? atoi(e) : 0; }();
     if (force_w == 4 && rpw > 1) W = 4;
+    // d_k = 128: 12 warps (24 rows) per CTA hide latency better than 8 and give 2 even waves on 148 SMs
+    if (KP == 128 && rpw == 2 && p.V >= 48 && force_w != 8) W = 12;
     for (;;) {
         c.W = W;
         c.TV = W * rpw;
         c.smem = bwd_smem_layout(KP, c.TV, c.s.RV * c.s.RK, 32 * W, W * VG, es, unc).total;
-        if (c.smem <= 227 * 1024 || W == 4 || rpw == 1) break;
+        if (c.smem <= 227 * 1024 || W == 4 || rpw == 1 || W == 12) break;
         W = 4;
     }
     return c;
@@ -797,6 +801,8 @@ template <int RK, int KG, int RV>
 static int launch_bwd_t(const BwdArgs& a, int tiles, int num_seg, bool carry_only, cudaStream_t stream) {
     const BwdConfig cfg = bwd_config(a.p);
     if (cfg.W == 8) return launch_bwd_w<RK, KG, RV, 8>(a, tiles, num_seg, carry_only, stream);
+    if constexpr (RK == 4 && KG == 32 && RV == 2)
+        if (cfg.W == 12) return launch_bwd_w<RK, KG, RV, 12>(a, tiles, num_seg, carry_only, stream);
     if constexpr (RV > 1) return launch_bwd_w<RK, KG, RV, 4>(a, tiles, num_seg, carry_only, stream);
     return PALIMPSA_E_DIM;
 }

@@ -74,9 +74,11 @@ def plan_segments(N: int, T: int, H: int, K: int, V: int) -> int:
     (and an extra state-gradient pass in backward), so they are only used when the (sequence, head,
     row-tile) grid alone would leave most of the 148 SMs idle, e.g. one very long sequence."""
     ctas = N * H * ((V + 15) // 16)
-    if ctas >= 148 or T < 1024:
+    if ctas >= 148 or T < 2048:
         return 1
-    return max(1, min((296 + ctas - 1) // ctas, T // 512))
+    # segments only cost a summary pass whose total work does not depend on their number, and shorter
+    # segments balance better over the SMs: cut down to about 4096 tokens, at most 32 pieces
+    return max(1, min(32, T // 1024))
 
 
 def segment_len(T: int, G: int) -> int:
