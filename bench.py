@@ -249,7 +249,9 @@ def kernel_roofline(d, cfg, steps, peaks):
     flops = 30.0 * K * V * th                        # algorithmic lane-ops of the backward, per the operator's definition
     achieved = alg_bytes / (ms * 1e-3) / 1e9
     return {"bound": "hbm", "kernel": "bwd_kernel (backward main)", "achieved": achieved, "peak": peaks["hbm_gbs"],
-            "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"], "traffic": None,
+            "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
+            # dram__bytes_read+write of one launch: ncu capture of the half batch (1 557.6 MB, profiles/), doubled
+            "traffic": 2 * 1557.6e6 * (th / 196608.0),
             "launch_ms": ms, "algorithmic_bytes_per_launch": alg_bytes,
             "note": "the kernel is FP32-pipe bound, not HBM bound: see 'compute'",
             "compute": {"algorithmic_tflops": flops / (ms * 1e-3) / 1e12, "flop_per_token_head": 30 * K * V}}
@@ -336,12 +338,67 @@ def run_ours(args, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
+def run_decode(args):
+    """Extra workload (not the headline): fused-recurrent decode, B=256 concurrent sequences with an fp32
+    (mu, I) state cache each (H=12, d_k=d_v=128), prefilled from a random 2048-token context, then
+    ``--decode-steps`` single-token bf16 steps on fresh seeded inputs.  Prints its own JSON line."""
+    from palimpsa_b200.ops import chunk_palimpsa, decode_step
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    B, H, K, V = C4["B"], C4["H"], C4["K"], C4["V"]
+    gen = torch.Generator(device=dev).manual_seed(0)
+    rn = lambda *s: torch.randn(*s, device=dev, generator=gen)
+    g = torch.nn.functional.softplus(rn(H))
+    Ip = torch.ones(H, device=dev)
+
+    def tokens(T):
+        q = torch.nn.functional.normalize(rn(B, T, H, K), dim=-1).bfloat16()
+        k = torch.nn.functional.normalize(rn(B, T, H, K), dim=-1).bfloat16()
+        return q, k, rn(B, T, H, V).bfloat16(), torch.sigmoid(rn(B, T, H, V)).bfloat16(), \
+            torch.nn.functional.softplus(rn(B, T, H))
+
+    mu = I = None
+    with torch.no_grad():
+        for _ in range(4):                                   # 2048-token context in four 512-token pieces
+            q, k, v, b, gt = tokens(512)
+            _, mu, I = chunk_palimpsa(q, k, v, b, gt, g, Ip, initial_mu_state=mu, initial_I_state=I,
+                                      output_final_state=True)
+    pool = [tokens(1) for _ in range(32)]                    # fresh inputs per step, cycled
+    steps = args.decode_steps
+    for i in range(20):
+        decode_step(*pool[i % 32], g, Ip, mu, I)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        decode_step(*pool[i % 32], g, Ip, mu, I)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    state_bytes = B * H * V * K * 4 * 2 * 2
+    peaks = measured_peaks()
+    gbs = state_bytes / (ms * 1e-3) / 1e9
+    print(json.dumps({"metric": "decode tokens/s (fused-recurrent, bf16 io, fp32 state)", "value": B / (ms * 1e-3),
+                      "unit": "tokens/s", "n_gpus": 1, "steps": steps, "ms_per_step": ms, "higher_is_better": True,
+                      "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": f"C4 decode B={B} H={H} d_k={K} d_v={V}, in-place state cache, "
+                                             f"prefill 2048 tokens"},
+                      "roofline": {"bound": "hbm", "kernel": "decode_kernel", "achieved": gbs, "peak": peaks["hbm_gbs"],
+                                   "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
+                                   "algorithmic_bytes_per_launch": state_bytes,
+                                   "traffic": 752.2e6},   # ncu: dram read 405.8 MB + write 346.3 MB
+                      "state_finite": bool(torch.isfinite(mu).all() and torch.isfinite(I).all())}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "decode"],
+                    help="c2 (default, the headline) or decode (extra line for the decode configuration)")
+    ap.add_argument("--decode-steps", type=int, default=1000)
     ap.add_argument("--profile-batch", type=int, default=4, help="batch size of --profile-case")
     ap.add_argument("--profile-segments", type=int, default=1,
                     help="with --profile-case: run one 32768-token sequence (H=12) cut into this many segments")
@@ -373,6 +430,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload == "decode":
+        if rank == 0:
+            run_decode(args)
         return
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
