@@ -1,22 +1,26 @@
 // Forward kernel of the Palimpsa operator (sm_100a).
 //
 // One CTA owns a tile of TV state rows (d_v) x all KP state columns (padded d_k) of one
-// (sequence, head) and walks that sequence's tokens in order with the (M, I) state pair held in
+// (sequence, head[, segment]) and walks its tokens in order with the (M, I) state pair held in
 // registers for the whole walk.  Work per state element and token: 6 packed-FP32 lane ops and one
 // MUFU reciprocal -- the kernel is bound by the MUFU pipe, not by HBM.
 //
-//   thread layout   lane = vg*KG + kg.  A thread owns RV=2 rows x RK columns; the KG lanes of a
-//                   row group own interleaved float4 column groups (column = 4*(j*KG+kg)+i), so
-//                   that shared-memory operand reads and global state accesses of a warp are
-//                   contiguous.
-//   staging         blocks of 16 tokens: cp.async (16 B) into a raw double buffer one block
-//                   ahead, then one cooperative pass converts to fp32 operands (q*scale, k, k*k,
-//                   v, b, f = exp(-gt*g), c = (1-f)*Ip) shared by every thread of the CTA.
-//   reduction       o[v] = sum_k: in-thread over RK, then log2(KG) xor-shuffles.
+//   thread layout   lane = vg*KG + kg.  A thread owns RV rows x RK columns; the KG lanes of a row
+//                   group own interleaved float4 column groups (column = 4*(j*KG+kg)+i), so that
+//                   shared-memory operand reads and global state accesses of a warp are contiguous.
+//                   Tile shapes are template parameters: every index in the hot loop is a constant.
+//   staging         blocks of 16 tokens: cp.async (16 B) into a raw double buffer one block ahead,
+//                   then one cooperative pass converts to fp32 operands (q*scale, k; v, b as
+//                   duplicated pairs; {f, f, c, c} with f = exp(-gt*g), c = (1-f)*Ip) shared by every
+//                   thread of the CTA.  k*k is formed in registers.
+//   reduction       o[v] = sum_k: in-thread over RK, then one transposed butterfly per 4 tokens over
+//                   the KG lanes of the row group.
 //   checkpoints     optional (M, I) store at the start of every 16-token block (for backward).
+//   segments        gridDim.z segments per sequence, each started from a given (M, I); the SUM
+//                   variant computes only the zero-start end state and decay of every segment.
 //
-// It serves the chunked op, the fused-recurrent op and the single-token decode step: what the
-// reference does with chunk_palimpsa_fwd_kernel (chunk_palimpsa_forgetting_scalar.py:66-218) and
+// It serves the chunked op and the fused-recurrent op: what the reference does with
+// chunk_palimpsa_fwd_kernel (chunk_palimpsa_forgetting_scalar.py:66-218) and
 // fused_palimpsa_recurrent_fwd_kernel (fused_recurrent_palimpsa.py:24-154).
 #include <cstdlib>
 
