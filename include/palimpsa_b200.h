@@ -37,7 +37,7 @@
 extern "C" {
 #endif
 
-#define PALIMPSA_ABI_VERSION 4
+#define PALIMPSA_ABI_VERSION 5
 
 /* io dtype of q, k, v, b, o, o_var, do, do_var, dq, dk, dv, db */
 #define PALIMPSA_F32 0
@@ -157,12 +157,24 @@ int palimpsa_cp_combine_bwd(const palimpsa_problem *p, const palimpsa_segments *
 int palimpsa_chunk_fwd_segments(const palimpsa_fwd_params *params, const palimpsa_segments *segs,
                                 void *cuda_stream);
 
-/* palimpsa_chunk_bwd per segment.  carry_only != 0: only propagate the state gradients from a zero
- * end-state gradient and write rloc_M/rloc_I (no other output is touched, no workspace needed).
- * carry_only == 0: full backward with segs->carry_M/carry_I (NULL = zero) as end-state gradients;
- * rloc_M/rloc_I, if given, receive the start-state gradients. */
+/* palimpsa_chunk_bwd per segment; `mode` selects the pass:
+ *   0  full backward with segs->carry_M/carry_I (NULL = zero) as end-state gradients; rloc_M/rloc_I, if
+ *      given, receive the start-state gradients;
+ *   1  state gradients only, from a zero end-state gradient: writes rloc_M/rloc_I and nothing else
+ *      (no workspace, no output buffers needed);
+ *   2  main kernel only with zero end-state gradients: every zero-carry gradient term plus rloc_M/rloc_I;
+ *      to be followed by palimpsa_cp_combine_bwd, palimpsa_carry_apply and mode 3;
+ *   3  the finishing kernels, including the partial slot palimpsa_carry_apply fills. */
 int palimpsa_chunk_bwd_segments(const palimpsa_bwd_params *params, const palimpsa_segments *segs,
-                                int carry_only, void *cuda_stream);
+                                int mode, void *cuda_stream);
+
+/* Adds the terms that are linear in the end-state gradients segs->carry_M/carry_I to a backward that
+ * ran with mode 2: dv, db are updated in place, the dk / dgt / dg / dIp terms go to a partial slot of
+ * the workspace that mode 3 sums.  Four [tokens x d]*[d x d] products per segment on the tensor cores
+ * (tcgen05, TMEM accumulators).  bf16 io without uncertainty output, d_v <= 128, padded d_k in
+ * {32,64,96,128}: palimpsa_carry_apply_supported() tells; otherwise use modes 1 and 0. */
+int palimpsa_carry_apply_supported(const palimpsa_problem *p);
+int palimpsa_carry_apply(const palimpsa_bwd_params *params, const palimpsa_segments *segs, void *cuda_stream);
 
 /* Version of this header the library was built from. */
 int palimpsa_abi_version(void);

@@ -7,7 +7,7 @@ import os
 PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libpalimpsa_b200.so")
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 F32, BF16, F16 = 0, 1, 2
 FLAG_UNCERTAINTY = 1
 FLAG_EXPLICIT_INIT = 2
@@ -72,6 +72,8 @@ SYMBOLS = {
                                           C.c_void_p, C.c_void_p]),
     "palimpsa_chunk_fwd_segments": (C.c_int, [C.POINTER(FwdParams), C.POINTER(Segments), C.c_void_p]),
     "palimpsa_chunk_bwd_segments": (C.c_int, [C.POINTER(BwdParams), C.POINTER(Segments), C.c_int, C.c_void_p]),
+    "palimpsa_carry_apply_supported": (C.c_int, [C.POINTER(Problem)]),
+    "palimpsa_carry_apply": (C.c_int, [C.POINTER(BwdParams), C.POINTER(Segments), C.c_void_p]),
     "palimpsa_chunk_fwd": (C.c_int, [C.POINTER(FwdParams), C.c_void_p]),
     "palimpsa_recurrent_fwd": (C.c_int, [C.POINTER(FwdParams), C.c_void_p]),
     "palimpsa_decode_step": (C.c_int, [C.POINTER(FwdParams), C.c_void_p]),

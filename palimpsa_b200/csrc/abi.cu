@@ -148,7 +148,22 @@ int palimpsa_segment_summary(const palimpsa_problem* p, const palimpsa_segments*
     return launch_fwd(&prm, sg, true, static_cast<cudaStream_t>(cuda_stream));
 }
 
-int palimpsa_tensor_core_status(void) { return summary_tc_status(); }
+int palimpsa_tensor_core_status(void) {
+    const int s = summary_tc_status();
+    return s ? s : carry_tc_status();
+}
+
+int palimpsa_carry_apply_supported(const palimpsa_problem* p) { return p && carry_tc_supported(*p) ? 1 : 0; }
+
+int palimpsa_carry_apply(const palimpsa_bwd_params* prm, const palimpsa_segments* sg, void* cuda_stream) {
+    int rc = check_bwd(prm);
+    if (rc) return rc;
+    rc = check_segments(prm->p, sg);
+    if (rc) return rc;
+    if (!sg->carry_M || !sg->carry_I) return PALIMPSA_E_NULL;
+    if (!carry_tc_supported(prm->p)) return PALIMPSA_E_DTYPE;
+    return launch_carry_tc(prm, *sg, static_cast<cudaStream_t>(cuda_stream));
+}
 
 int palimpsa_cp_combine(const palimpsa_problem* p, const palimpsa_segments* sg, const float* in_M, const float* in_J,
                         float* out_M, float* out_J, void* cuda_stream) {
@@ -185,16 +200,25 @@ int palimpsa_chunk_fwd_segments(const palimpsa_fwd_params* prm, const palimpsa_s
     return launch_fwd(prm, sg, false, static_cast<cudaStream_t>(cuda_stream));
 }
 
-int palimpsa_chunk_bwd_segments(const palimpsa_bwd_params* prm, const palimpsa_segments* sg, int carry_only,
+int palimpsa_chunk_bwd_segments(const palimpsa_bwd_params* prm, const palimpsa_segments* sg, int mode,
                                 void* cuda_stream) {
-    int rc = check_bwd(prm, carry_only == 0, carry_only == 0);
+    if (mode < 0 || mode > 3) return PALIMPSA_E_SHAPE;
+    const bool carry_only = mode == 1;
+    int rc = check_bwd(prm, !carry_only, !carry_only);
     if (rc) return rc;
     rc = check_segments(prm->p, sg);
     if (rc) return rc;
     if ((sg->carry_M == nullptr) != (sg->carry_I == nullptr) || (sg->rloc_M == nullptr) != (sg->rloc_I == nullptr))
         return PALIMPSA_E_NULL;
-    if (carry_only && !sg->rloc_M) return PALIMPSA_E_NULL;
-    return launch_bwd(prm, sg, carry_only != 0, static_cast<cudaStream_t>(cuda_stream), 3);
+    if ((mode == 1 || mode == 2) && !sg->rloc_M) return PALIMPSA_E_NULL;
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    if (mode == 2) {  // main kernel only, zero end-state gradients
+        palimpsa_segments z = *sg;
+        z.carry_M = z.carry_I = nullptr;
+        return launch_bwd(prm, &z, false, st, 1);
+    }
+    if (mode == 3) return launch_bwd(prm, sg, false, st, 2 | 4);  // finishing kernels, extra slot included
+    return launch_bwd(prm, sg, carry_only, st, 3);
 }
 
 size_t palimpsa_bwd_workspace_bytes(const palimpsa_problem* p) {

@@ -634,7 +634,7 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
 __global__ void bwd_finish_rows(const palimpsa_problem p, const float* __restrict__ dq_part,
                                 const float* __restrict__ dk_part, const float* __restrict__ df_part,
                                 const float* __restrict__ dip_part, void* dq, void* dk, float* dgt, float* w_dg,
-                                float* w_dip, int tiles, int KP, long long rows) {
+                                float* w_dip, int tiles, int tiles_k, int KP, long long rows) {
     const int lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -642,11 +642,14 @@ __global__ void bwd_finish_rows(const palimpsa_problem p, const float* __restric
     const int KP2 = KP / 2;
     for (int pi = lane; pi < KP2; pi += 32) {
         float2 sq = make_float2(0.f, 0.f), sk = sq;
-        for (int t = 0; t < tiles; ++t) {
+        for (int t = 0; t < tiles_k; ++t) {  // dk may have one slot more than dq: the carried-gradient terms
             const size_t e = ((size_t)t * rows + row) * KP2 + pi;
-            const float2 x = reinterpret_cast<const float2*>(dq_part)[e];
+            if (t < tiles) {
+                const float2 x = reinterpret_cast<const float2*>(dq_part)[e];
+                sq.x += x.x, sq.y += x.y;
+            }
             const float2 y = reinterpret_cast<const float2*>(dk_part)[e];
-            sq.x += x.x, sq.y += x.y, sk.x += y.x, sk.y += y.y;
+            sk.x += y.x, sk.y += y.y;
         }
         const int kc = 2 * pi;
         if (kc < p.K) {
@@ -660,7 +663,7 @@ __global__ void bwd_finish_rows(const palimpsa_problem p, const float* __restric
     }
     if (lane == 0) {
         float df = 0.f, dip = 0.f;
-        for (int t = 0; t < tiles; ++t) {
+        for (int t = 0; t < tiles_k; ++t) {
             df += df_part[(size_t)t * rows + row];
             dip += dip_part[(size_t)t * rows + row];
         }
@@ -763,9 +766,10 @@ BwdWorkspace bwd_workspace_layout(const palimpsa_problem& p) {
         return o;
     };
     ws.dq_part = take((size_t)ws.tiles * rows * ws.KP * 4);
-    ws.dk_part = take((size_t)ws.tiles * rows * ws.KP * 4);
-    ws.df_part = take((size_t)ws.tiles * rows * 4);
-    ws.dip_part = take((size_t)ws.tiles * rows * 4);
+    // one slot more than there are row tiles: the carried-gradient terms of a segmented backward go there
+    ws.dk_part = take((size_t)(ws.tiles + 1) * rows * ws.KP * 4);
+    ws.df_part = take((size_t)(ws.tiles + 1) * rows * 4);
+    ws.dip_part = take((size_t)(ws.tiles + 1) * rows * 4);
     ws.w_dg = take(rows * 4);
     ws.w_dip = take(rows * 4);
     ws.total = off;
@@ -861,7 +865,8 @@ int launch_bwd(const palimpsa_bwd_params* prm, const palimpsa_segments* segs, bo
         const int wpb = 8;
         bwd_finish_rows<<<(unsigned)((rows + wpb - 1) / wpb), 32 * wpb, 0, stream>>>(
             p, a.dq_part, a.dk_part, a.df_part, a.dip_part, prm->dq, prm->dk, prm->dgt,
-            reinterpret_cast<float*>(base + ws.w_dg), reinterpret_cast<float*>(base + ws.w_dip), ws.tiles, ws.KP, rows);
+            reinterpret_cast<float*>(base + ws.w_dg), reinterpret_cast<float*>(base + ws.w_dip), ws.tiles,
+            ws.tiles + ((stages & 4) ? 1 : 0), ws.KP, rows);
         if (cudaGetLastError() != cudaSuccess) return PALIMPSA_E_LAUNCH;
     }
     bwd_finish_heads<<<p.H, 256, 0, stream>>>(reinterpret_cast<float*>(base + ws.w_dg),

@@ -16,7 +16,8 @@ int launch_fwd(const palimpsa_fwd_params* prm, const palimpsa_segments* segs, bo
 bool decode_supported(const palimpsa_fwd_params* prm);
 int launch_decode(const palimpsa_fwd_params* prm, cudaStream_t stream);
 
-// Backward (bwd.cu): main kernel (stages bit 0) + the two finishing kernels (bit 1).
+// Backward (bwd.cu): main kernel (stages bit 0) + the two finishing kernels (bit 1); bit 2: the finishing
+// kernels also sum the extra partial slot that carry_tc.cu fills.
 int launch_bwd(const palimpsa_bwd_params* prm, const palimpsa_segments* segs, bool carry_only, cudaStream_t stream,
                int stages);
 
@@ -24,6 +25,11 @@ int launch_bwd(const palimpsa_bwd_params* prm, const palimpsa_segments* segs, bo
 bool summary_tc_supported(const palimpsa_problem& p);
 int launch_summary_tc(const palimpsa_problem& p, const palimpsa_segments& segs, cudaStream_t stream);
 int summary_tc_status();
+
+// Carried-gradient terms of a segmented backward on the tensor cores (carry_tc.cu).
+bool carry_tc_supported(const palimpsa_problem& p);
+int launch_carry_tc(const palimpsa_bwd_params* prm, const palimpsa_segments& segs, cudaStream_t stream);
+int carry_tc_status();
 
 // Boundary scans over segments (segments.cu).
 int launch_combine_fwd(const palimpsa_problem& p, const palimpsa_segments& segs, const float* in_M, const float* in_J,
@@ -39,7 +45,7 @@ int bwd_tile_rows(const palimpsa_problem& p);
 
 // Layout of the backward scratch memory (byte offsets from a 256-byte aligned base).
 struct BwdWorkspace {
-    size_t dq_part, dk_part;    // float [tiles][tokens*H][KP]
+    size_t dq_part, dk_part;    // float [tiles][tokens*H][KP]   (dk, df, dip: tiles + 1 slots)
     size_t df_part, dip_part;   // float [tiles][tokens*H]
     size_t w_dg, w_dip;         // float [tokens*H]
     size_t total;

@@ -7,6 +7,7 @@ stream.  There is no fallback: CPU tensors are rejected and a missing library ra
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -206,11 +207,23 @@ def bwd_op(do: Tensor, do_var: Optional[Tensor], q: Tensor, k: Tensor, v: Tensor
             sg, bufs = make_segments(B, G, segment_len(T, G), H, V, K, dev, fwd=False)
             sg.decay = seg_decay.data_ptr()
             st = _stream(q)
-            L.check(lib.palimpsa_chunk_bwd_segments(C.byref(prm), C.byref(sg), 1, st), "palimpsa backward (carry pass)")
-            L.check(lib.palimpsa_cp_combine_bwd(C.byref(prm.p), C.byref(sg), None, None, None, None, st),
-                    "palimpsa boundary scan (backward)")
-            sg.rloc_M = sg.rloc_I = None
-            L.check(lib.palimpsa_chunk_bwd_segments(C.byref(prm), C.byref(sg), 0, st), "palimpsa backward (segments)")
+            if lib.palimpsa_carry_apply_supported(C.byref(prm.p)) and not os.environ.get("PALIMPSA_CARRY_SIMT"):
+                # zero-carry backward of every segment -> reverse boundary scan -> carried terms on the tensor
+                # cores -> finishing kernels
+                L.check(lib.palimpsa_chunk_bwd_segments(C.byref(prm), C.byref(sg), 2, st), "palimpsa backward (main)")
+                L.check(lib.palimpsa_cp_combine_bwd(C.byref(prm.p), C.byref(sg), None, None, None, None, st),
+                        "palimpsa boundary scan (backward)")
+                L.check(lib.palimpsa_carry_apply(C.byref(prm), C.byref(sg), st), "palimpsa carried-gradient terms")
+                L.check(lib.palimpsa_chunk_bwd_segments(C.byref(prm), C.byref(sg), 3, st), "palimpsa backward (finish)")
+            else:
+                # state-gradient pass per segment -> reverse boundary scan -> full backward per segment
+                L.check(lib.palimpsa_chunk_bwd_segments(C.byref(prm), C.byref(sg), 1, st),
+                        "palimpsa backward (carry pass)")
+                L.check(lib.palimpsa_cp_combine_bwd(C.byref(prm.p), C.byref(sg), None, None, None, None, st),
+                        "palimpsa boundary scan (backward)")
+                sg.rloc_M = sg.rloc_I = None
+                L.check(lib.palimpsa_chunk_bwd_segments(C.byref(prm), C.byref(sg), 0, st),
+                        "palimpsa backward (segments)")
         else:
             fn = lib.palimpsa_recurrent_bwd if recurrent else lib.palimpsa_chunk_bwd
             L.check(fn(C.byref(prm), _stream(q)), "palimpsa backward")

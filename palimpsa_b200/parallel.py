@@ -170,7 +170,7 @@ class _CudaLocal:
                                                  out[1].data_ptr(), self.stream), "boundary scan (backward)")
         return out
 
-    def backward(self, do, ckM, ckI, sg):
+    def _outs(self, do, ckM, ckI):
         q, k, v, b, gt, g, Ip = self.t
         outs = [torch.empty_like(q), torch.empty_like(k), torch.empty_like(v), torch.empty_like(b),
                 torch.empty(self.N, self.T, self.H, dtype=torch.float32, device=self.dev),
@@ -179,10 +179,30 @@ class _CudaLocal:
         prm = self._bwd_params(do, ckM, ckI)
         need = self.lib.palimpsa_bwd_workspace_bytes(C.byref(prm.p))
         ws = torch.empty(max(need, 256), dtype=torch.uint8, device=self.dev)
-        prm = self._bwd_params(do, ckM, ckI, outs, ws)
+        return outs, ws, self._bwd_params(do, ckM, ckI, outs, ws)
+
+    def tensor_core_carry(self) -> bool:
+        import os
+        return bool(self.lib.palimpsa_carry_apply_supported(C.byref(self.prob))) and \
+            not os.environ.get("PALIMPSA_CARRY_SIMT")
+
+    def backward(self, do, ckM, ckI, sg):
+        """Full backward of every local segment with the end-state gradients in sg.carry_*."""
+        outs, ws, prm = self._outs(do, ckM, ckI)
         sg.rloc_M = sg.rloc_I = None
         L.check(self.lib.palimpsa_chunk_bwd_segments(C.byref(prm), C.byref(sg), 0, self.stream), "backward (segments)")
         return outs
+
+    def backward_main(self, do, ckM, ckI, sg):
+        """Tensor-core path, step 1: zero-carry backward of every local segment (+ start-state gradients)."""
+        outs, ws, prm = self._outs(do, ckM, ckI)
+        L.check(self.lib.palimpsa_chunk_bwd_segments(C.byref(prm), C.byref(sg), 2, self.stream), "backward (main)")
+        return outs, ws, prm
+
+    def backward_finish(self, prm, sg):
+        """Tensor-core path, step 2 (after the chain): carried terms as GEMMs, then the finishing kernels."""
+        L.check(self.lib.palimpsa_carry_apply(C.byref(prm), C.byref(sg), self.stream), "carried-gradient terms")
+        L.check(self.lib.palimpsa_chunk_bwd_segments(C.byref(prm), C.byref(sg), 3, self.stream), "backward (finish)")
 
 
 class _CpChunkPalimpsa(torch.autograd.Function):
@@ -209,9 +229,16 @@ class _CpChunkPalimpsa(torch.autograd.Function):
         do = do.to(loc.t[0].dtype).contiguous()
         with torch.cuda.device(do.device):
             sg, bufs = loc.bwd_segments(decay)
-            loc.bwd_carry(do, ckM, ckI, sg)                  # zero-carry state gradients of every segment
-            chain_up(ctx.rank, ctx.world, ctx.group, lambda inc: loc.combine_bwd(sg, inc), loc.state_like())
-            dq, dk, dv, db, dgt, dg, dIp = loc.backward(do, ckM, ckI, sg)
+            if loc.tensor_core_carry():
+                # the heavy pass needs no remote data: it runs BEFORE the chain, on all ranks at once
+                outs, ws, prm = loc.backward_main(do, ckM, ckI, sg)
+                chain_up(ctx.rank, ctx.world, ctx.group, lambda inc: loc.combine_bwd(sg, inc), loc.state_like())
+                loc.backward_finish(prm, sg)
+                dq, dk, dv, db, dgt, dg, dIp = outs
+            else:
+                loc.bwd_carry(do, ckM, ckI, sg)              # zero-carry state gradients of every segment
+                chain_up(ctx.rank, ctx.world, ctx.group, lambda inc: loc.combine_bwd(sg, inc), loc.state_like())
+                dq, dk, dv, db, dgt, dg, dIp = loc.backward(do, ckM, ckI, sg)
             if ctx.reduce and ctx.world > 1:
                 pg = torch.stack([dg, dIp])
                 dist.all_reduce(pg, group=ctx.group)

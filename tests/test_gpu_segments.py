@@ -64,3 +64,29 @@ def test_auto_plan_uses_segments_only_when_starved():
     assert plan_segments(8, 4096, 6, 128, 128) == 1       # 170M-shaped batch: the grid already fills the GPU
     assert plan_segments(1, 131072, 12, 128, 128) == 32   # one long sequence: 96 CTAs -> 32 segments of 4096
     assert plan_segments(1, 512, 2, 64, 64) == 1
+
+
+def test_tensor_core_carry_terms_match_oracle_and_cuda_core_path(monkeypatch):
+    """bf16: the carried-gradient terms computed with tcgen05 GEMMs equal the two-pass CUDA-core path and the
+    float64 oracle within the bf16 bound; no bounded wait gave up."""
+    from palimpsa_b200 import _lib as L
+    inp = orc.make_inputs(17, B=2, T=700, H=2, K=128, V=128, dtype=torch.bfloat16)
+    inp["gt"] = inp["gt"] * 0.05            # slow decay (0.9 .. 0.99): the carried terms are large
+    ref = run_oracle(inp)
+    tc_path = _run(inp, 5)
+    assert L.lib().palimpsa_tensor_core_status() == 0
+    monkeypatch.setenv("PALIMPSA_CARRY_SIMT", "1")
+    simt = _run(inp, 5)
+    compare(tc_path, ref, TOL_BF16, what="tensor-core carry vs oracle")
+    compare(simt, ref, TOL_BF16, what="CUDA-core carry vs oracle")
+    for n in ("dk", "dv", "db", "dgt", "dg", "dIp"):
+        assert orc.rel_err(tc_path[n], simt[n]) < 1e-2, n
+
+
+@pytest.mark.parametrize("K,V,T,G", [(64, 128, 300, 3), (128, 64, 260, 2), (32, 48, 130, 2)])
+def test_tensor_core_carry_other_shapes(K, V, T, G):
+    inp = orc.make_inputs(K + V + T, B=1, T=T, H=2, K=K, V=V, dtype=torch.bfloat16)
+    inp["gt"] = inp["gt"] * 0.05
+    got = _run(inp, G)
+    ref = run_oracle(inp)
+    compare(got, ref, TOL_BF16, what=f"tensor-core carry K={K} V={V}")
