@@ -55,6 +55,10 @@ struct BwdSmem {
     int total;
 };
 
+// Buffers for the d_k-indexed partials of a token group: two (one barrier per group instead of two) where
+// the shared memory allows it, i.e. up to 8 warps and d_k <= 128.
+__host__ __device__ constexpr int bwd_kred_buffers(int nthr, int KP) { return (nthr > 256 || KP > 128) ? 1 : 2; }
+
 // Shared-memory plan of one backward CTA (KP padded d_k, TV state rows, NE state elements per thread,
 // WV row groups).  Operand tiles v, b, dy are stored with every value duplicated ({x, x}) so that a
 // 64-bit load yields the register pair the packed FP32 instructions want.
@@ -81,7 +85,7 @@ __host__ __device__ inline BwdSmem bwd_smem_layout(int KP, int TV, int NE, int n
     s.slots = take(2 * 2 * NE * nthr * 4);
     s.ck_stage = 2 * TV * KP * 4;
     s.ckb = take(2 * s.ck_stage);
-    s.kred = take((nthr > 256 ? 1 : 2) * GR * WV * 2 * KP * 4);  // two group buffers (one barrier per group) if they fit
+    s.kred = take(bwd_kred_buffers(nthr, KP) * GR * WV * 2 * KP * 4);
     s.raw = off;
     int r = 0;
     auto rtake = [&](int bytes) {
@@ -237,7 +241,7 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
     constexpr int KP = RK * KG, VG = 32 / KG, NP = RK / 2, NE = RV * RK, KP2 = KP / 2;
     constexpr int TV = W * VG * RV, WV = W * VG, NTHR = 32 * W;
     constexpr int NG = TB / GR;       // groups per block
-    constexpr int KBUF = NTHR > 256 ? 1 : 2;  // shared-memory buffers for the d_k-indexed partials
+    constexpr int KBUF = bwd_kred_buffers(NTHR, KP);  // shared-memory buffers for the d_k-indexed partials
     constexpr int NR1 = GR * RV * 2;  // per-group d_v-indexed partials of a thread: (token, row, dv|db)
     constexpr int NR2 = GR * 2;       // per-group per-token scalars: (token, df|sum GI)
     extern __shared__ __align__(16) unsigned char sm[];

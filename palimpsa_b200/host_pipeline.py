@@ -9,7 +9,7 @@ see device tensors; it exists because end-to-end throughput from host buffers is
 """
 from __future__ import annotations
 
-from typing import Dict, Optional
+from typing import Dict, Optional, Sequence, Union
 
 import torch
 
@@ -19,16 +19,42 @@ _IN_BATCHED = ("q", "k", "v", "b", "gt", "do")
 _OUT_BATCHED = ("o", "dq", "dk", "dv", "db", "dgt")
 
 
+def ramped_widths(batch: int, middle: int = 2):
+    """Slice widths ``1, middle, ..., middle, 1`` covering ``batch`` sequences (fewer, wider slices keep
+    the kernels' grids full; the single-sequence slices at both ends keep the exposed copies short)."""
+    if batch <= 2:
+        return [1] * batch
+    inner, widths = batch - 2, [1]
+    while inner > 0:
+        w = min(middle, inner)
+        widths.append(w)
+        inner -= w
+    return widths + [1]
+
+
 class HostPipeline:
     """Reusable pipeline for one problem shape.  ``run(host)`` takes pinned CPU tensors ``q,k,v,b,do``
     ``[B,T,H,*]``, ``gt [B,T,H]``, ``g,Ip [H]`` and returns pinned CPU tensors ``o, dq, dk, dv, db, dgt,
     dg, dIp``; it returns after everything has landed on the host."""
 
-    def __init__(self, host: Dict[str, torch.Tensor], device, slices: int = 4):
+    def __init__(self, host: Dict[str, torch.Tensor], device, slices: Union[int, Sequence[int]] = 4):
+        """``slices``: a count (even split of the batch) or the slice widths themselves, e.g. ``(1, 2, 2,
+        2, 1)``: a narrow first slice starts the compute early and a narrow last one shortens the final
+        download, which is all of the copy time that cannot hide behind compute."""
         self.dev = torch.device(device)
         B = host["q"].shape[0]
-        self.slices = max(1, min(slices, B))
-        self.bounds = [(i * B // self.slices, (i + 1) * B // self.slices) for i in range(self.slices)]
+        if isinstance(slices, int):
+            n = max(1, min(slices, B))
+            widths = [(i + 1) * B // n - i * B // n for i in range(n)]
+        else:
+            widths = [int(w) for w in slices]
+            if not widths or min(widths) < 1 or sum(widths) != B:
+                raise ValueError(f"slice widths {widths} must be positive and sum to the batch size {B}")
+        self.slices = len(widths)
+        self.bounds, lo = [], 0
+        for w in widths:
+            self.bounds.append((lo, lo + w))
+            lo += w
         width = max(hi - lo for lo, hi in self.bounds)
         # two staging slots: slice i+1 uploads while slice i computes
         self.slots = [{n: torch.empty((width,) + tuple(host[n].shape[1:]), dtype=host[n].dtype, device=self.dev)
@@ -95,7 +121,7 @@ class HostPipeline:
         return self.out
 
 
-def fwd_bwd_from_host(host: Dict[str, torch.Tensor], device, slices: int = 4, scale=None,
+def fwd_bwd_from_host(host: Dict[str, torch.Tensor], device, slices: Union[int, Sequence[int]] = 4, scale=None,
                       pipeline: Optional[HostPipeline] = None) -> Dict[str, torch.Tensor]:
     """One-shot convenience wrapper; pass ``pipeline`` to reuse staging buffers across calls."""
     pipe = pipeline or HostPipeline(host, device, slices)

@@ -72,14 +72,15 @@ def _chunk_offsets(cu_seqlens: Tensor) -> Tensor:
 
 def plan_segments(N: int, T: int, H: int, K: int, V: int) -> int:
     """How many segments to cut every sequence into on one GPU.  Segments cost an extra summary pass
-    (and an extra state-gradient pass in backward), so they are only used when the (sequence, head,
-    row-tile) grid alone would leave most of the 148 SMs idle, e.g. one very long sequence."""
+    (and the carried-gradient terms in backward), so they are only used when the (sequence, head,
+    row-tile) grid alone would leave SMs idle, e.g. one very long sequence or a narrow batch slice."""
     ctas = N * H * ((V + 15) // 16)
     if ctas >= 148 or T < 2048:
         return 1
-    # segments only cost a summary pass whose total work does not depend on their number, and shorter
-    # segments balance better over the SMs: cut down to about 4096 tokens, at most 32 pieces
-    return max(1, min(32, T // 1024))
+    # The boundary passes' total work does not depend on the number of segments, and their own grids
+    # (one CTA per sequence x head x segment) want many of them: cut down to 256 tokens, at most 32 pieces
+    # (measured flat from 16 to 128 pieces on T = 4096 .. 32768).
+    return max(1, min(32, T // 256))
 
 
 def segment_len(T: int, G: int) -> int:

@@ -21,7 +21,9 @@ from oracle.palimpsa_oracle import make_inputs, make_states  # noqa: E402
 
 
 def _ref():
-    root = os.environ.get("PALIMPSA_REFERENCE", "/root/reference")
+    root = os.environ.get("PALIMPSA_REFERENCE")
+    if not root or not os.path.isdir(os.path.join(root, "palimpsa")):
+        raise SystemExit("set PALIMPSA_REFERENCE to the root of a checkout of the reference project")
     sys.path.insert(0, root)
     from palimpsa.ops.palimpsa import palimpsa_ref
     return palimpsa_ref

@@ -60,11 +60,17 @@ def test_shipped_head_shapes(K, V, dtype):
     compare(got, ref, tol_for(dtype), what=f"K={K} V={V} {dtype}")
 
 
-def test_k256_forward_only():
-    inp = orc.make_inputs(1, B=1, T=40, H=2, K=256, V=16)
-    got = run_cuda(inp, "chunk", grads=False)
-    ref = run_oracle(inp)
-    compare(got, ref, TOL_FP32, names=["o", "final_mu", "final_I"], what="K=256")
+@pytest.mark.parametrize("dtype,unc", [(torch.float32, False), (torch.float32, True), (torch.bfloat16, True)])
+def test_k256(dtype, unc):
+    """The widest supported d_k: one state row per thread column group, 8-row tiles in the backward."""
+    inp = orc.make_inputs(1, B=2, T=70, H=2, K=256, V=24, dtype=dtype)
+    got = run_cuda(inp, "chunk", unc=unc)
+    ref = run_oracle(inp, unc=unc)
+    compare(got, ref, tol_for(dtype), what=f"K=256 {dtype} unc={unc}")
+    inp = orc.make_inputs(2, B=1, T=33, H=1, K=200, V=5, dtype=dtype)
+    got = run_cuda(inp, "chunk", unc=unc)
+    ref = run_oracle(inp, unc=unc)
+    compare(got, ref, tol_for(dtype), what=f"K=200 {dtype} unc={unc}")
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])

@@ -63,6 +63,7 @@ def test_auto_plan_uses_segments_only_when_starved():
     from palimpsa_b200.ops.palimpsa._core import plan_segments
     assert plan_segments(8, 4096, 6, 128, 128) == 1       # 170M-shaped batch: the grid already fills the GPU
     assert plan_segments(1, 131072, 12, 128, 128) == 32   # one long sequence: 96 CTAs -> 32 segments of 4096
+    assert plan_segments(1, 4096, 6, 128, 128) == 16      # a one-sequence slice: 256-token segments
     assert plan_segments(1, 512, 2, 64, 64) == 1
 
 
