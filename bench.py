@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the Palimpsa operator hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c4]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|decode|layer]
 
 Workload (default ``c2``): the 170M-model-shaped layer op, chunked forward + backward in bf16 with
 fp32 state, B=8, T=4096, H=6, d_k=d_v=128, seeded synthetic inputs (q,k L2-normalised N(0,1);
@@ -159,8 +159,8 @@ def cpu_baseline(budget_s, cfg, steps=1, warmup=0):
 def run_reference(args, rank, world):
     if rank != 0:
         return
-    cores = torch.get_num_threads()
     val, sample, times = cpu_baseline(150.0, C2, steps=args.steps, warmup=args.warmup)
+    cores = torch.get_num_threads()                   # as set by cpu_baseline: every host core
     ms = 1e3 * sum(times) / len(times)
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
@@ -331,7 +331,11 @@ def run_ours(args, rank, world, local_rank):
                                 "frac_of_fp32_peak": roof["compute"]["algorithmic_tflops"] / fp["fma_tflops"]})
     del d
     torch.cuda.empty_cache()
-    cb_val, cb_sample, _ = cpu_baseline(20.0, cfg, steps=2, warmup=0)
+    cpu_line = None                                   # the CPU port is timed beside the one-GPU run only
+    if world == 1:
+        cb_val, cb_sample, _ = cpu_baseline(20.0, cfg, steps=2, warmup=0)
+        cpu_line = {"value": cb_val, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                    "sample": cb_sample}
     line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -343,8 +347,7 @@ def run_ours(args, rank, world, local_rank):
                     "ms_per_step": ms_e2e / e2e_steps, "api": "palimpsa_b200.host_pipeline.HostPipeline.run",
                     "batch_slices": slices, "slice_widths": [hi - lo for lo, hi in pipe.bounds]},
             "gpu_launches": 4 * args.steps + per_e2e_step * (e2e_steps + 3), "clocks": clocks, "roofline": roof,
-            "cpu_baseline": {"value": cb_val, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-                             "sample": cb_sample}}
+            "cpu_baseline": cpu_line}
     print(json.dumps(line), flush=True)
 
 
@@ -400,14 +403,129 @@ def run_decode(args):
                       "state_finite": bool(torch.isfinite(mu).all() and torch.isfinite(I).all())}), flush=True)
 
 
+def run_layer(args):
+    """Extra workload (not the headline): the layer's element-wise prologue and epilogue around the operator on
+    the C2 shapes (B=8 T=4096 H=6 d_k=d_v=128, bf16), forward and backward, as four fused kernels.  Each is
+    timed alone with CUDA events (inputs 200-600 MB per launch, above L2) and compared with the same lines
+    written as the layer writes them, in eager PyTorch on the same GPU.  Prints its own JSON line."""
+    import torch.nn.functional as F
+    from palimpsa_b200 import _lib
+    from palimpsa_b200.layers import layer_epilogue, layer_prologue
+    _lib.lib()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    B, T, H, K, V = C2["B"], C2["T"], C2["H"], C2["K"], C2["V"]
+    gen = torch.Generator(device="cpu").manual_seed(0)
+    r = lambda *sh: torch.randn(*sh, generator=gen).to(dev, torch.bfloat16)
+    q_raw, k_raw, x, b_raw, gate, o = r(B, T, H, K), r(B, T, H, K), r(B, T, H, V), r(B, T, H, V), r(B, T, H, V), r(B, T, H, V)
+    dt_raw, bs_raw = r(B, T, H), r(B, T, H)
+    dt_bias, b_scale = torch.randn(H, generator=gen).to(dev), torch.ones(H, device=dev)
+    D, weight = torch.ones(H, device=dev), torch.ones(V, device=dev)
+    cot = [r(B, T, H, K), r(B, T, H, K), r(B, T, H, V), r(B, T, H, V), torch.randn(B, T, H, generator=gen).to(dev)]
+    dy = r(B, T, H, V)
+    peaks = measured_peaks()
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    # the four fused passes, each timed alone through the C ABI (structs built once: no host work in the loop)
+    import ctypes as C
+    from palimpsa_b200 import layers as LY
+    lib = _lib.lib()
+    sp = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    pa = LY._prologue_struct(q_raw, k_raw, x, b_raw, dt_raw, bs_raw, dt_bias, b_scale)
+    pouts = [torch.empty_like(q_raw), torch.empty_like(k_raw), torch.empty_like(x), torch.empty_like(x),
+             torch.empty(B, T, H, device=dev)]
+    pa.q, pa.k, pa.v, pa.b, pa.gt = [t.data_ptr() for t in pouts]
+    pa.dq, pa.dk, pa.dv, pa.db, pa.dgt = [t.data_ptr() for t in cot]
+    pgr = [torch.empty_like(q_raw), torch.empty_like(k_raw), torch.empty_like(x), torch.empty_like(x),
+           torch.empty_like(dt_raw), torch.empty_like(bs_raw), torch.empty(H, device=dev), torch.empty(H, device=dev)]
+    pa.dq_raw, pa.dk_raw, pa.dx, pa.db_raw, pa.ddt_raw, pa.dbs_raw, pa.d_dt_bias, pa.d_b_scale = \
+        [t.data_ptr() for t in pgr]
+    ws = LY._workspace(B * T, H, V, dev)
+    pa.workspace, pa.workspace_bytes = ws.data_ptr(), ws.numel()
+    ea = LY._Epilogue._struct(o, x, D, weight, gate, 1e-5)
+    eouts = [torch.empty_like(o) for _ in range(4)]
+    egr = [torch.empty(H, device=dev), torch.empty(V, device=dev)]
+    ea.y, ea.d_o, ea.dx, ea.dgate = [t.data_ptr() for t in eouts]
+    ea.dy, ea.dD, ea.dweight = dy.data_ptr(), egr[0].data_ptr(), egr[1].data_ptr()
+    ea.workspace, ea.workspace_bytes = ws.data_ptr(), ws.numel()
+    n = max(5, args.steps)
+    t_pf = timed(lambda: _lib.check(lib.palimpsa_layer_prologue_fwd(C.byref(pa), sp), "prologue"), n)
+    t_pb = timed(lambda: _lib.check(lib.palimpsa_layer_prologue_bwd(C.byref(pa), sp), "prologue bwd"), n)
+    t_ef = timed(lambda: _lib.check(lib.palimpsa_layer_epilogue_fwd(C.byref(ea), sp), "epilogue"), n)
+    t_eb = timed(lambda: _lib.check(lib.palimpsa_layer_epilogue_bwd(C.byref(ea), sp), "epilogue bwd"), n)
+
+    pin = [t.detach().requires_grad_(True) for t in (q_raw, k_raw, x, b_raw, dt_raw, bs_raw, dt_bias, b_scale)]
+    ein = [t.detach().requires_grad_(True) for t in (o, x, D, weight, gate)]
+
+    def ours_fb():                                    # the same work through the public, differentiable API
+        for t in pin + ein:
+            t.grad = None
+        torch.autograd.backward(layer_prologue(*pin), cot)
+        layer_epilogue(*ein).backward(dy)
+
+    t_api = timed(ours_fb, n)
+
+    def eager_fb():                                   # the layer's own lines (layers/palimpsa.py:269-281, 337-343)
+        for t in pin + ein:
+            t.grad = None
+        qr, kr, xx, br, dtr, bsr, dtb, bsc = pin
+        dt = F.softplus(dtr.float() + dtb)
+        q, k = F.normalize(qr, p=2, dim=-1), F.normalize(kr, p=2, dim=-1)
+        bs = torch.sigmoid(bsr.float()).to(xx.dtype)
+        v = xx * bs.unsqueeze(-1)
+        b = torch.sigmoid(br.float()) * F.softplus(bsc.view(1, 1, -1, 1).float())
+        b = (b * bs.unsqueeze(-1)).to(xx.dtype)
+        torch.autograd.backward([q, k, v, b, dt], cot)
+        oo, x2, DD, ww, gg = ein
+        z = (oo + x2 * DD[None, None, :, None]).float()
+        y = z * torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + 1e-5) * ww
+        y = (y * gg.float() * torch.sigmoid(gg.float())).to(oo.dtype)
+        y.backward(dy)
+
+    t_eager = timed(eager_fb, n)
+    rows, es = B * T * H, 2
+    alg = {"prologue_fwd": rows * ((4 * K + 4 * V) * es + 2 * es + 4),
+           "prologue_bwd": rows * ((6 * K + 6 * V) * es + 4 * es + 4 + 8),
+           "epilogue_fwd": rows * 4 * V * es,
+           "epilogue_bwd": rows * (7 * V * es + 4)}
+    ms = {"prologue_fwd": t_pf, "prologue_bwd": t_pb, "epilogue_fwd": t_ef, "epilogue_bwd": t_eb}
+    kernels = {k2: {"ms": ms[k2], "algorithmic_bytes": alg[k2], "GB/s": alg[k2] / ms[k2] / 1e6,
+                    "frac_of_hbm_peak": alg[k2] / ms[k2] / 1e6 / peaks["hbm_gbs"]} for k2 in ms}
+    total = sum(ms.values())
+    top = max(ms, key=ms.get)
+    line = {"metric": "layer element-wise prologue+epilogue fwd+bwd tokens/s (bf16, T=4096)", "value": B * T / (total * 1e-3),
+            "unit": "tokens/s", "n_gpus": 1, "steps": n, "warmup": 3, "ms_per_step": total, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"layer element-wise sides on C2 shapes B={B} T={T} H={H} d_k={K} d_v={V} bf16",
+                       "l2": "every launch moves 200-600 MB, above L2"},
+            "gpu_launches": 4 * (n + 3) + 7 * (n + 3), "kernels": kernels, "public_api_fwd_bwd_ms": t_api,
+            "torch_eager_fwd_bwd_ms": t_eager,
+            "roofline": {"bound": "hbm", "kernel": top, "achieved": kernels[top]["GB/s"], "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": kernels[top]["frac_of_hbm_peak"], "peak_source": peaks["source"],
+                         "traffic": None}}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c2", "decode"],
-                    help="c2 (default, the headline) or decode (extra line for the decode configuration)")
+    ap.add_argument("--workload", default="c2", choices=["c2", "decode", "layer"],
+                    help="c2 (default, the headline), decode (extra line for the decode configuration) or layer "
+                         "(extra line for the fused element-wise kernels around the operator)")
     ap.add_argument("--decode-steps", type=int, default=1000)
     ap.add_argument("--profile-batch", type=int, default=4, help="batch size of --profile-case")
     ap.add_argument("--profile-segments", type=int, default=1,
@@ -440,6 +558,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload == "layer":
+        if rank == 0:
+            run_layer(args)
         return
     if args.workload == "decode":
         if rank == 0:

@@ -37,7 +37,7 @@
 extern "C" {
 #endif
 
-#define PALIMPSA_ABI_VERSION 5
+#define PALIMPSA_ABI_VERSION 6
 
 /* io dtype of q, k, v, b, o, o_var, do, do_var, dq, dk, dv, db */
 #define PALIMPSA_F32 0
@@ -232,6 +232,72 @@ int palimpsa_chunk_bwd_static(const palimpsa_bwd_params *params, void *cuda_stre
 
 /* Backward of the fused-recurrent op (absent in the reference: fused_recurrent_palimpsa.py:250-253). */
 int palimpsa_recurrent_bwd(const palimpsa_bwd_params *params, void *cuda_stream);
+
+/* ---- Layer-side element-wise work around the operator ---------------------------------------------
+ * The reference's layer prepares the operator's inputs and post-processes its output with a dozen
+ * separate PyTorch element-wise passes (palimpsa/layers/palimpsa.py:269-283 and :337-344).  These
+ * entry points do each side in ONE pass over HBM.  Arithmetic is float32 with a single rounding to the
+ * io dtype, except bs, which is rounded to the io dtype before use exactly as the layer does (:272).
+ * All tensors are contiguous; `tokens` counts every token of the (packed) batch. */
+
+/* Prologue (layers/palimpsa.py:269-281):
+ *     gt = softplus(dt_raw + dt_bias[h])            q = q_raw / max(|q_raw|_2, 1e-12)   (same for k)
+ *     bs = sigmoid(bs_raw)  (rounded to io dtype)    v = x * bs
+ *     b  = sigmoid(b_raw) * softplus(b_scale[h]) * bs
+ * q_raw / k_raw carry Hq <= H heads (H % Hq == 0); head h reads head h / (H/Hq) (the layer's repeat, :266). */
+typedef struct palimpsa_layer_prologue {
+    size_t struct_size;
+    int32_t io_dtype;            /* PALIMPSA_F32 / BF16 / F16                                      */
+    int32_t H, Hq, K, V;         /* K <= 256, V <= 1024                                             */
+    int64_t tokens;
+    const void *q_raw, *k_raw;   /* [tokens,Hq,K] io dtype                                          */
+    const void *x, *b_raw;       /* [tokens,H,V]  io dtype                                          */
+    const void *dt_raw, *bs_raw; /* [tokens,H]    io dtype                                          */
+    const float *dt_bias, *b_scale; /* [H] float32                                                  */
+    void *q, *k;                 /* out [tokens,H,K] io dtype                                       */
+    void *v, *b;                 /* out [tokens,H,V] io dtype                                       */
+    float *gt;                   /* out [tokens,H] float32                                          */
+    /* backward only */
+    const void *dq, *dk, *dv, *db; /* gradients w.r.t. the outputs above, io dtype                  */
+    const float *dgt;            /* [tokens,H] float32                                              */
+    void *dq_raw, *dk_raw;       /* out [tokens,Hq,K] io dtype                                      */
+    void *dx, *db_raw;           /* out [tokens,H,V]  io dtype (dx: the v = x*bs branch only)       */
+    void *ddt_raw, *dbs_raw;     /* out [tokens,H]    io dtype                                      */
+    float *d_dt_bias, *d_b_scale;/* out [H] float32, summed over tokens in a fixed order            */
+    void *workspace;             /* backward scratch, >= palimpsa_layer_workspace_bytes()           */
+    size_t workspace_bytes;
+} palimpsa_layer_prologue;
+
+/* Epilogue (layers/palimpsa.py:337-343; the gated RMS norm is FusedRMSNormGated of the pinned
+ * dependency flash-linear-attention 0.5.1, activation "swish"):
+ *     z = o + x * D[h]   (PALIMPSA_LAYER_RESIDUAL)        r = 1 / sqrt(mean_v(z^2) + eps)
+ *     y = z * r * weight[v] * gate * sigmoid(gate)        (PALIMPSA_LAYER_GATE; else y = z * r * weight[v]) */
+#define PALIMPSA_LAYER_RESIDUAL 1u
+#define PALIMPSA_LAYER_GATE 2u
+typedef struct palimpsa_layer_epilogue {
+    size_t struct_size;
+    int32_t io_dtype;
+    int32_t H, V;                /* V <= 1024                                                       */
+    uint32_t flags;
+    float eps;
+    int64_t tokens;
+    const void *o, *x, *gate;    /* [tokens,H,V] io dtype (x / gate may be NULL without their flag) */
+    const float *D, *weight;     /* [H], [V] float32                                                */
+    void *y;                     /* out [tokens,H,V] io dtype                                       */
+    /* backward only */
+    const void *dy;              /* [tokens,H,V] io dtype                                           */
+    void *d_o, *dx, *dgate;      /* out [tokens,H,V] io dtype (dx: the residual branch only)        */
+    float *dD, *dweight;         /* out [H], [V] float32, summed in a fixed order                   */
+    void *workspace;
+    size_t workspace_bytes;
+} palimpsa_layer_epilogue;
+
+/* Scratch either backward needs for `tokens` x H rows of width V (the larger of the two). */
+size_t palimpsa_layer_workspace_bytes(int64_t tokens, int32_t H, int32_t V);
+int palimpsa_layer_prologue_fwd(const palimpsa_layer_prologue *a, void *cuda_stream);
+int palimpsa_layer_prologue_bwd(const palimpsa_layer_prologue *a, void *cuda_stream);
+int palimpsa_layer_epilogue_fwd(const palimpsa_layer_epilogue *a, void *cuda_stream);
+int palimpsa_layer_epilogue_bwd(const palimpsa_layer_epilogue *a, void *cuda_stream);
 
 #ifdef __cplusplus
 }

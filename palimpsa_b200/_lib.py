@@ -7,7 +7,7 @@ import os
 PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libpalimpsa_b200.so")
 
-ABI_VERSION = 5
+ABI_VERSION = 6
 F32, BF16, F16 = 0, 1, 2
 FLAG_UNCERTAINTY = 1
 FLAG_EXPLICIT_INIT = 2
@@ -58,6 +58,37 @@ class Segments(C.Structure):
     ]
 
 
+LAYER_RESIDUAL, LAYER_GATE = 1, 2
+
+
+class LayerPrologue(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_size_t), ("io_dtype", C.c_int32),
+        ("H", C.c_int32), ("Hq", C.c_int32), ("K", C.c_int32), ("V", C.c_int32),
+        ("tokens", C.c_int64),
+        ("q_raw", C.c_void_p), ("k_raw", C.c_void_p), ("x", C.c_void_p), ("b_raw", C.c_void_p),
+        ("dt_raw", C.c_void_p), ("bs_raw", C.c_void_p), ("dt_bias", C.c_void_p), ("b_scale", C.c_void_p),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("b", C.c_void_p), ("gt", C.c_void_p),
+        ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p), ("db", C.c_void_p), ("dgt", C.c_void_p),
+        ("dq_raw", C.c_void_p), ("dk_raw", C.c_void_p), ("dx", C.c_void_p), ("db_raw", C.c_void_p),
+        ("ddt_raw", C.c_void_p), ("dbs_raw", C.c_void_p), ("d_dt_bias", C.c_void_p), ("d_b_scale", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class LayerEpilogue(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_size_t), ("io_dtype", C.c_int32),
+        ("H", C.c_int32), ("V", C.c_int32), ("flags", C.c_uint32), ("eps", C.c_float),
+        ("tokens", C.c_int64),
+        ("o", C.c_void_p), ("x", C.c_void_p), ("gate", C.c_void_p), ("D", C.c_void_p), ("weight", C.c_void_p),
+        ("y", C.c_void_p),
+        ("dy", C.c_void_p), ("d_o", C.c_void_p), ("dx", C.c_void_p), ("dgate", C.c_void_p),
+        ("dD", C.c_void_p), ("dweight", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
 # every symbol include/palimpsa_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "palimpsa_abi_version": (C.c_int, []),
@@ -82,6 +113,11 @@ SYMBOLS = {
     "palimpsa_chunk_bwd_stages": (C.c_int, [C.POINTER(BwdParams), C.c_void_p, C.c_int]),
     "palimpsa_chunk_bwd_static": (C.c_int, [C.POINTER(BwdParams), C.c_void_p]),
     "palimpsa_recurrent_bwd": (C.c_int, [C.POINTER(BwdParams), C.c_void_p]),
+    "palimpsa_layer_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32]),
+    "palimpsa_layer_prologue_fwd": (C.c_int, [C.POINTER(LayerPrologue), C.c_void_p]),
+    "palimpsa_layer_prologue_bwd": (C.c_int, [C.POINTER(LayerPrologue), C.c_void_p]),
+    "palimpsa_layer_epilogue_fwd": (C.c_int, [C.POINTER(LayerEpilogue), C.c_void_p]),
+    "palimpsa_layer_epilogue_bwd": (C.c_int, [C.POINTER(LayerEpilogue), C.c_void_p]),
 }
 
 _lib = None

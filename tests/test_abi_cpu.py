@@ -39,8 +39,11 @@ def test_struct_layout_matches_c(L, tmp_path):
     fields_b = [f[0] for f in L.BwdParams._fields_]
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(){"]
     fields_s = [f[0] for f in L.Segments._fields_]
+    fields_lp = [f[0] for f in L.LayerPrologue._fields_]
+    fields_le = [f[0] for f in L.LayerEpilogue._fields_]
     for st, fl in (("palimpsa_problem", fields_p), ("palimpsa_fwd_params", fields_f), ("palimpsa_bwd_params", fields_b),
-                   ("palimpsa_segments", fields_s)):
+                   ("palimpsa_segments", fields_s), ("palimpsa_layer_prologue", fields_lp),
+                   ("palimpsa_layer_epilogue", fields_le)):
         lines.append(f'printf("%zu\\n", sizeof({st}));')
         for f in fl:
             lines.append(f'printf("%zu\\n", offsetof({st}, {f}));')
@@ -50,7 +53,7 @@ def test_struct_layout_matches_c(L, tmp_path):
     subprocess.check_call(["gcc", "-std=c99", "-Wall", "-Werror", str(prog), "-o", str(exe)])
     nums = [int(x) for x in subprocess.check_output([str(exe)]).split()]
     it = iter(nums)
-    for cls in (L.Problem, L.FwdParams, L.BwdParams, L.Segments):
+    for cls in (L.Problem, L.FwdParams, L.BwdParams, L.Segments, L.LayerPrologue, L.LayerEpilogue):
         assert next(it) == C.sizeof(cls)
         for f in cls._fields_:
             assert next(it) == getattr(cls, f[0]).offset, (cls.__name__, f[0])
