@@ -47,8 +47,13 @@ def build(force: bool = False, verbose: bool = False) -> str:
     objdir = os.path.join(PKG, "build")
     os.makedirs(objdir, exist_ok=True)
 
+    headers = [s for s in _sources() if not s.endswith(".cu")]
+
     def compile_unit(u):
         obj = os.path.join(objdir, u + ".o")
+        deps = headers + [os.path.join(CSRC, u + ".cu")]
+        if not force and os.path.exists(obj) and all(os.path.getmtime(d) <= os.path.getmtime(obj) for d in deps):
+            return obj                                # this unit's sources are older than its object
         cmd = [_nvcc(), *NVCC_FLAGS, "-c", os.path.join(CSRC, u + ".cu"), "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         with open(os.path.join(objdir, u + ".ptxas.log"), "w") as f:
