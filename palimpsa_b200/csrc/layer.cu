@@ -14,8 +14,8 @@ namespace palimpsa {
 
 namespace {
 
-constexpr float NORM_EPS = 1e-12f;   // F.normalize's default eps
-constexpr float NORM_EPS2 = 1e-24f;  // its square: 1/max(sqrt(s), eps) = rsqrt(max(s, eps^2))
+// F.normalize clamps the norm at eps = 1e-12; in squares: 1/max(sqrt(s), eps) = rsqrt(max(s, eps^2))
+constexpr float NORM_EPS2 = 1e-24f;
 
 __device__ __forceinline__ float warp_sum(float x) {
 #pragma unroll
@@ -301,11 +301,15 @@ __global__ void __launch_bounds__(256, min_ctas(NCK * NCV, 3)) layer_prologue_bw
     }
 }
 
-// out[h] = sum over tokens of w[token*H + h], in a fixed order (one CTA of 1024 threads per head; every
-// thread sums a strided subsequence with 8 loads in flight, then a tree over the CTA).
-__global__ void __launch_bounds__(1024) layer_sum_heads_kernel(const float* __restrict__ w, float* __restrict__ out,
+// out[h] = sum over tokens of w[token*H + h] in a fixed order, for up to two arrays at once (blockIdx.y picks
+// the array): one CTA of 1024 threads per head; every thread sums a strided subsequence with 8 loads in
+// flight, then a tree over the CTA.
+__global__ void __launch_bounds__(1024) layer_sum_heads_kernel(const float* __restrict__ w0, float* __restrict__ out0,
+                                                               const float* __restrict__ w1, float* __restrict__ out1,
                                                                long long tokens, int H) {
     __shared__ float red[1024];
+    const float* __restrict__ w = blockIdx.y ? w1 : w0;
+    float* __restrict__ out = blockIdx.y ? out1 : out0;
     const int h = blockIdx.x;
     float s = 0.f;
     long long t = threadIdx.x;
@@ -523,12 +527,29 @@ __global__ void __launch_bounds__(1024) layer_sum_cols_kernel(const float* __res
 namespace {
 
 constexpr int LAYER_MAX_V = 1024;
-constexpr int DW_CTAS = 148 * 4;  // partial rows of dweight (persistent CTAs of the epilogue backward)
+constexpr int DW_CTAS = 1024;  // capacity for the partial rows of dweight (one per persistent CTA of the epilogue backward)
 
 bool aligned_for(const void* p, int dt) { return (reinterpret_cast<uintptr_t>(p) & (dt == PALIMPSA_F32 ? 15 : 7)) == 0; }
-unsigned row_blocks(long long warps, int cap) {
-    long long b = (warps + 7) / 8;
-    return (unsigned)(b < 1 ? 1 : (b > cap ? cap : b));
+int sm_count() {
+    static const int n = [] {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+            v = 148;
+        return v;
+    }();
+    return n;
+}
+// CTAs of 8 warps for `warps` warp-rows: at most `waves` full waves of the kernel's resident CTAs (the
+// kernels loop over the rest), so that no partial wave trails behind.
+template <class Kern>
+unsigned row_blocks(Kern kern, long long warps, size_t smem, int waves, int cap = 1 << 30) {
+    int occ = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, 256, smem) != cudaSuccess || occ < 1) occ = 1;
+    long long full = (long long)sm_count() * occ * waves;
+    if (full > cap) full = cap;
+    const long long b = (warps + 7) / 8;
+    return (unsigned)(b < 1 ? 1 : (b > full ? full : b));
 }
 size_t ws_bytes(long long tokens, int H, int V) {
     const size_t rows = (size_t)tokens * H;
@@ -579,40 +600,56 @@ int launched() { return cudaGetLastError() == cudaSuccess ? PALIMPSA_OK : PALIMP
 template <int DT, int NCK, int NCV>
 void pro_fwd_launch(const palimpsa_layer_prologue& a, int rows, bool veck, bool vecv, cudaStream_t st) {
     constexpr int R = (NCK == 1 && NCV == 1) ? 2 : 1;
-    const unsigned nb = row_blocks((rows + R - 1) / R, 148 * 8);
     const size_t sm = (size_t)a.H * sizeof(float);
-    if (veck && vecv)
-        layer_prologue_fwd_kernel<DT, NCK, NCV, R, true, true><<<nb, 256, sm, st>>>(a, rows);
-    else
-        layer_prologue_fwd_kernel<DT, NCK, NCV, R, false, false><<<nb, 256, sm, st>>>(a, rows);
+    const long long warps = (rows + R - 1) / R;
+    if (veck && vecv) {
+        auto kern = layer_prologue_fwd_kernel<DT, NCK, NCV, R, true, true>;
+        kern<<<row_blocks(kern, warps, sm, 2), 256, sm, st>>>(a, rows);
+    } else {
+        auto kern = layer_prologue_fwd_kernel<DT, NCK, NCV, R, false, false>;
+        kern<<<row_blocks(kern, warps, sm, 2), 256, sm, st>>>(a, rows);
+    }
 }
 template <int DT, int NCK, int NCV>
 void pro_bwd_launch(const palimpsa_layer_prologue& a, int qrows, bool veck, bool vecv, float* w0, float* w1,
                     cudaStream_t st) {
-    const unsigned nb = row_blocks(qrows, 148 * 6);
     const size_t sm = 2 * (size_t)a.H * sizeof(float);
-    if (veck && vecv)
-        layer_prologue_bwd_kernel<DT, NCK, NCV, true, true><<<nb, 256, sm, st>>>(a, qrows, w0, w1);
-    else
-        layer_prologue_bwd_kernel<DT, NCK, NCV, false, false><<<nb, 256, sm, st>>>(a, qrows, w0, w1);
+    if (veck && vecv) {
+        auto kern = layer_prologue_bwd_kernel<DT, NCK, NCV, true, true>;
+        kern<<<row_blocks(kern, qrows, sm, 2), 256, sm, st>>>(a, qrows, w0, w1);
+    } else {
+        auto kern = layer_prologue_bwd_kernel<DT, NCK, NCV, false, false>;
+        kern<<<row_blocks(kern, qrows, sm, 2), 256, sm, st>>>(a, qrows, w0, w1);
+    }
 }
 template <int DT, int NC>
 void epi_fwd_launch(const palimpsa_layer_epilogue& a, int rows, bool vecv, cudaStream_t st) {
     constexpr int R = NC == 1 ? 2 : 1;
-    const unsigned nb = row_blocks((rows + R - 1) / R, 148 * 8);
-    if (vecv)
-        layer_epilogue_fwd_kernel<DT, NC, R, true><<<nb, 256, 0, st>>>(a, rows);
-    else
-        layer_epilogue_fwd_kernel<DT, NC, R, false><<<nb, 256, 0, st>>>(a, rows);
+    const long long warps = (rows + R - 1) / R;
+    if (vecv) {
+        auto kern = layer_epilogue_fwd_kernel<DT, NC, R, true>;
+        kern<<<row_blocks(kern, warps, 0, 2), 256, 0, st>>>(a, rows);
+    } else {
+        auto kern = layer_epilogue_fwd_kernel<DT, NC, R, false>;
+        kern<<<row_blocks(kern, warps, 0, 2), 256, 0, st>>>(a, rows);
+    }
 }
+// returns the number of CTAs launched = partial rows of dweight written (one resident wave, at most DW_CTAS)
 template <int DT, int NC>
-void epi_bwd_launch(const palimpsa_layer_epilogue& a, int rows, bool vecv, float* w0, float* w1, unsigned nb,
-                    cudaStream_t st) {
+unsigned epi_bwd_launch(const palimpsa_layer_epilogue& a, int rows, bool vecv, float* w0, float* w1, cudaStream_t st) {
     constexpr int R = NC == 1 ? 2 : 1;
-    if (vecv)
-        layer_epilogue_bwd_kernel<DT, NC, R, true><<<nb, 256, 0, st>>>(a, rows, w0, w1);
-    else
-        layer_epilogue_bwd_kernel<DT, NC, R, false><<<nb, 256, 0, st>>>(a, rows, w0, w1);
+    const long long warps = (rows + R - 1) / R;
+    unsigned nb;
+    if (vecv) {
+        auto kern = layer_epilogue_bwd_kernel<DT, NC, R, true>;
+        nb = row_blocks(kern, warps, 0, 1, DW_CTAS);
+        kern<<<nb, 256, 0, st>>>(a, rows, w0, w1);
+    } else {
+        auto kern = layer_epilogue_bwd_kernel<DT, NC, R, false>;
+        nb = row_blocks(kern, warps, 0, 1, DW_CTAS);
+        kern<<<nb, 256, 0, st>>>(a, rows, w0, w1);
+    }
+    return nb;
 }
 
 #define PALIMPSA_BY_DTYPE(dt, CALL)                                   \
@@ -698,8 +735,7 @@ int palimpsa_layer_prologue_bwd(const palimpsa_layer_prologue* a, void* cuda_str
 #undef CALL_V
         if (int rc = launched()) return rc;
     }
-    layer_sum_heads_kernel<<<a->H, 1024, 0, st>>>(w_dtb, a->d_dt_bias, a->tokens, a->H);
-    layer_sum_heads_kernel<<<a->H, 1024, 0, st>>>(w_bsc, a->d_b_scale, a->tokens, a->H);
+    layer_sum_heads_kernel<<<dim3(a->H, 2), 1024, 0, st>>>(w_dtb, a->d_dt_bias, w_bsc, a->d_b_scale, a->tokens, a->H);
     return launched();
 }
 
@@ -733,13 +769,13 @@ int palimpsa_layer_epilogue_bwd(const palimpsa_layer_epilogue* a, void* cuda_str
     float* w_dD = reinterpret_cast<float*>(a->workspace);
     float* w_dw = w_dD + rows;
     const int nc = (a->V + 127) / 128;
-    const unsigned nb = row_blocks(nc == 1 ? (rows + 1) / 2 : rows, DW_CTAS);
+    unsigned nb = 0;
     if (rows > 0) {
         const int dt = a->io_dtype;
         const bool vecv = a->V % 4 == 0 && aligned_for(a->o, dt) && aligned_for(a->dy, dt) && aligned_for(a->d_o, dt) &&
                           (!res || (aligned_for(a->x, dt) && aligned_for(a->dx, dt))) &&
                           (!gated || (aligned_for(a->gate, dt) && aligned_for(a->dgate, dt)));
-#define CALL_V(NV) epi_bwd_launch<DTX, NV>(*a, rows, vecv, w_dD, w_dw, nb, st)
+#define CALL_V(NV) nb = epi_bwd_launch<DTX, NV>(*a, rows, vecv, w_dD, w_dw, st)
 #define CALL_D(D)                     \
     do {                              \
         constexpr int DTX = D;        \
@@ -750,8 +786,8 @@ int palimpsa_layer_epilogue_bwd(const palimpsa_layer_epilogue* a, void* cuda_str
 #undef CALL_V
         if (int rc = launched()) return rc;
     }
-    if (res) layer_sum_heads_kernel<<<a->H, 1024, 0, st>>>(w_dD, a->dD, a->tokens, a->H);
-    layer_sum_cols_kernel<<<(a->V + 31) / 32, 1024, 0, st>>>(w_dw, a->dweight, rows > 0 ? (int)nb : 0, a->V);
+    if (res) layer_sum_heads_kernel<<<dim3(a->H, 1), 1024, 0, st>>>(w_dD, a->dD, w_dD, a->dD, a->tokens, a->H);
+    layer_sum_cols_kernel<<<(a->V + 31) / 32, 1024, 0, st>>>(w_dw, a->dweight, (int)nb, a->V);
     return launched();
 }
 
