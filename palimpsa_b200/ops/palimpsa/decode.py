@@ -49,3 +49,48 @@ def decode_step(q, k, v, b, gt, g, Ip, mu_state: torch.Tensor, I_state: torch.Te
         prm.final_mu, prm.final_I = mu_state.data_ptr(), I_state.data_ptr()
         L.check(lib.palimpsa_decode_step(C.byref(prm), _core._stream(q)), "palimpsa decode step")
     return (o, o_var) if output_uncertainty else o
+
+
+class DecodeGraph:
+    """``decode_step`` captured once in a CUDA graph and replayed per token: the step then costs one graph
+    launch instead of the Python-side argument handling and kernel launch.  The graph reads its inputs from
+    static buffers (``self.q, k, v, b, gt``: fill them, or pass tensors to :meth:`step`, which copies) and
+    updates ``mu_state`` / ``I_state`` in place; ``self.o`` (and ``self.o_var``) hold the latest outputs and
+    are overwritten by the next replay."""
+
+    def __init__(self, g, Ip, mu_state: torch.Tensor, I_state: torch.Tensor, dtype=torch.bfloat16,
+                 scale: Optional[float] = None, output_uncertainty: bool = False):
+        N, H, V, K = mu_state.shape
+        dev = mu_state.device
+        _core._require_cuda(g, Ip, mu_state, I_state)
+        self.q = torch.zeros(N, 1, H, K, dtype=dtype, device=dev)
+        self.k = torch.zeros_like(self.q)
+        self.v = torch.zeros(N, 1, H, V, dtype=dtype, device=dev)
+        self.b = torch.zeros_like(self.v)
+        self.gt = torch.zeros(N, 1, H, dtype=torch.float32, device=dev)
+        self.g, self.Ip = g.detach().float().contiguous(), Ip.detach().float().contiguous()
+        self.mu_state, self.I_state = mu_state, I_state
+        self.unc = output_uncertainty
+        L.lib()                                        # load (and fail) outside the capture
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            # zero inputs are an identity update only for f = 1, so the warm-up runs on copies of the cache
+            mu_tmp, I_tmp = mu_state.clone(), I_state.clone()
+            decode_step(self.q, self.k, self.v, self.b, self.gt, self.g, self.Ip, mu_tmp, I_tmp, scale,
+                        output_uncertainty)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        with torch.cuda.graph(self.graph):
+            out = decode_step(self.q, self.k, self.v, self.b, self.gt, self.g, self.Ip, mu_state, I_state, scale,
+                              output_uncertainty)
+        self.o, self.o_var = out if output_uncertainty else (out, None)
+
+    def step(self, q=None, k=None, v=None, b=None, gt=None):
+        """Copies the given tensors into the static input buffers (those left ``None`` keep their content) and
+        replays the graph on the current stream.  Returns ``self.o`` (and ``self.o_var``)."""
+        for dst, src in ((self.q, q), (self.k, k), (self.v, v), (self.b, b), (self.gt, gt)):
+            if src is not None:
+                dst.copy_(src.reshape(dst.shape), non_blocking=True)
+        self.graph.replay()
+        return (self.o, self.o_var) if self.unc else self.o

@@ -39,3 +39,22 @@ def test_decode_steps_match_oracle(K, V, dtype):
                                                output_final_state=True)
     assert torch.equal(o2, outs[-1])
     assert torch.equal(mu2, mu) and torch.equal(I2, I)
+
+
+def test_graph_replay_equals_eager_decode():
+    """The step captured in a CUDA graph: same outputs and same cache as step-by-step launches, bit for bit."""
+    from palimpsa_b200.ops import DecodeGraph, decode_step, fused_recurrent_palimpsa
+    N, H, K, V, T0, steps = 4, 3, 64, 64, 12, 8
+    inp = orc.make_inputs(77, B=N, T=T0 + steps, H=H, K=K, V=V, dtype=torch.bfloat16)
+    d = {n: inp[n].to(DEV) for n in ("q", "k", "v", "b", "gt", "g", "Ip")}
+    sl = lambda a, b: {n: (x[:, a:b] if x.dim() >= 3 else x) for n, x in d.items()}
+    _, mu, I = fused_recurrent_palimpsa(**sl(0, T0), output_final_state=True)
+    mu_g, I_g = mu.clone(), I.clone()
+    dec = DecodeGraph(d["g"], d["Ip"], mu_g, I_g, dtype=torch.bfloat16, output_uncertainty=True)
+    assert torch.equal(mu_g, mu) and torch.equal(I_g, I)          # building the graph leaves the cache alone
+    for t in range(T0, T0 + steps):
+        o, ov = decode_step(**sl(t, t + 1), mu_state=mu, I_state=I, output_uncertainty=True)
+        tok = sl(t, t + 1)
+        og, ovg = dec.step(tok["q"], tok["k"], tok["v"], tok["b"], tok["gt"])
+        assert torch.equal(og, o) and torch.equal(ovg, ov), t
+    assert torch.equal(mu_g, mu) and torch.equal(I_g, I)
