@@ -89,7 +89,8 @@ def chain_up(rank: int, world: int, group, local: Callable[[Optional[torch.Tenso
 class _CudaLocal:
     """One rank's share of the sequence, driven through the C ABI (segment entry points)."""
 
-    def __init__(self, q, k, v, b, gt, g, Ip, scale, num_segments, first_rank: bool):
+    def __init__(self, q, k, v, b, gt, g, Ip, scale, num_segments, first_rank: bool, init_mu=None, init_I=None,
+                 uncertainty: bool = False):
         from .ops.palimpsa import _core
         self.core = _core
         self.lib = L.lib()
@@ -103,8 +104,13 @@ class _CudaLocal:
         self.first = first_rank
         self.dev = q.device
         self.stream = _core._stream(q)
+        self.do_var = None                               # gradient of the uncertainty output, set by backward
         self.sg, self.bufs = _core.make_segments(self.N, self.G, self.seg_len, self.H, self.V, self.K, self.dev, True)
-        self.prob = _core._problem(q, k, v, b, gt, g, Ip, None, None, None, None, self.scale, 0)
+        self.unc = uncertainty
+        # only the rank that holds the start of the sequence knows an explicit initial state
+        self.init = (init_mu, init_I) if first_rank and init_mu is not None else (None, None)
+        self.prob = _core._problem(q, k, v, b, gt, g, Ip, None, None, self.init[0], self.init[1], self.scale,
+                                   L.FLAG_UNCERTAINTY if uncertainty else 0)
 
     def state_like(self):
         return torch.empty(2, self.N, self.H, self.V, self.KP, dtype=torch.float32, device=self.dev)
@@ -123,6 +129,7 @@ class _CudaLocal:
         q, k, v, b, gt, g, Ip = self.t
         core = self.core
         o = torch.empty(self.N, self.T, self.H, self.V, dtype=q.dtype, device=self.dev)
+        o_var = torch.empty_like(o) if self.unc else None
         fmu = torch.empty(self.N, self.H, self.V, self.K, dtype=torch.float32, device=self.dev)
         fI = torch.empty_like(fmu)
         ckM = ckI = None
@@ -133,11 +140,11 @@ class _CudaLocal:
         prm = L.FwdParams()
         prm.struct_size = C.sizeof(L.FwdParams)
         prm.p = self.prob
-        prm.o = core._ptr(o)
+        prm.o, prm.o_var = core._ptr(o), core._ptr(o_var)
         prm.final_mu, prm.final_I = fmu.data_ptr(), fI.data_ptr()
         prm.ckpt_M, prm.ckpt_I = core._ptr(ckM), core._ptr(ckI)
         L.check(self.lib.palimpsa_chunk_fwd_segments(C.byref(prm), C.byref(self.sg), self.stream), "forward (segments)")
-        return o, fmu, fI, ckM, ckI
+        return o, o_var, fmu, fI, ckM, ckI
 
     # ---- backward ----
     def _bwd_params(self, do, ckM, ckI, outs=None, ws=None):
@@ -147,7 +154,7 @@ class _CudaLocal:
         prm.p = self.prob
         if not self.first:
             prm.p.flags |= L.FLAG_EXPLICIT_INIT      # this rank starts from a received state, not from the prior
-        prm.d_o = core._ptr(do)
+        prm.d_o, prm.d_o_var = core._ptr(do), core._ptr(self.do_var)
         prm.ckpt_M, prm.ckpt_I = ckM.data_ptr(), ckI.data_ptr()
         if outs is not None:
             prm.dq, prm.dk, prm.dv, prm.db, prm.dgt, prm.dg, prm.dIp = [core._ptr(x) for x in outs]
@@ -207,26 +214,34 @@ class _CudaLocal:
 
 class _CpChunkPalimpsa(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, b, gt, g, Ip, scale, group, num_segments, reduce_param_grads):
+    def forward(ctx, q, k, v, b, gt, g, Ip, scale, group, num_segments, reduce_param_grads, init_mu, init_I,
+                uncertainty):
         rank, world = dist.get_rank(group), dist.get_world_size(group)
-        loc = _CudaLocal(q, k, v, b, gt, g, Ip, scale, num_segments, first_rank=(rank == 0))
+        loc = _CudaLocal(q, k, v, b, gt, g, Ip, scale, num_segments, first_rank=(rank == 0), init_mu=init_mu,
+                         init_I=init_I, uncertainty=uncertainty)
         need_grad = any(ctx.needs_input_grad[:7])
         with torch.cuda.device(q.device):
             loc.summary()                                    # no dependence on other ranks
             chain_down(rank, world, group, loc.combine, loc.state_like())
-            o, fmu, fI, ckM, ckI = loc.forward(save_ckpt=need_grad)
+            o, o_var, fmu, fI, ckM, ckI = loc.forward(save_ckpt=need_grad)
         ctx.loc, ctx.group, ctx.reduce = loc, group, reduce_param_grads
         ctx.rank, ctx.world = rank, world
         if need_grad:
             ctx.save_for_backward(ckM, ckI, loc.bufs["decay"])
         ctx.mark_non_differentiable(fmu, fI)
-        return o, fmu, fI
+        if o_var is None:
+            o_var = o.new_empty(0)
+            ctx.mark_non_differentiable(o_var)
+        return o, o_var, fmu, fI
 
     @staticmethod
-    def backward(ctx, do, _dmu, _dI):
+    def backward(ctx, do, do_var, _dmu, _dI):
         loc = ctx.loc
         ckM, ckI, decay = ctx.saved_tensors
-        do = do.to(loc.t[0].dtype).contiguous()
+        io = loc.t[0].dtype
+        do = torch.zeros_like(loc.t[2]) if do is None else do.to(io).contiguous()
+        if loc.unc:
+            loc.do_var = torch.zeros_like(do) if do_var is None else do_var.to(io).contiguous()
         with torch.cuda.device(do.device):
             sg, bufs = loc.bwd_segments(decay)
             if loc.tensor_core_carry():
@@ -243,16 +258,19 @@ class _CpChunkPalimpsa(torch.autograd.Function):
                 pg = torch.stack([dg, dIp])
                 dist.all_reduce(pg, group=ctx.group)
                 dg, dIp = pg[0], pg[1]
-        return dq, dk, dv, db, dgt, dg, dIp, None, None, None, None
+        return dq, dk, dv, db, dgt, dg, dIp, None, None, None, None, None, None, None
 
 
 def cp_chunk_palimpsa(q, k, v, b, gt, g, Ip, group=None, scale=None, output_final_state=False, num_segments=None,
-                      reduce_param_grads=True):
+                      reduce_param_grads=True, initial_mu_state=None, initial_I_state=None,
+                      output_uncertainty=False):
     """Context-parallel ``chunk_palimpsa``: every rank of ``group`` passes ITS contiguous share of the
     sequence (``q,k [B,T_local,H,K]`` ...; shares in rank order; lengths may differ) and gets its share of
     ``o`` and of the gradients.  With ``output_final_state`` also returns the state after this rank's
     last token (the sequence's final state on the last rank).  ``dg`` / ``dIp`` are summed over the group
-    unless ``reduce_param_grads=False``.  The sequence starts from the prior (no explicit initial state)."""
+    unless ``reduce_param_grads=False``.  ``initial_mu_state`` / ``initial_I_state`` ``[B,H,V,K]`` (both or
+    neither) are the state before the sequence's first token: only the first rank's are used, and they get
+    no gradient, as in ``chunk_palimpsa``.  ``output_uncertainty`` returns ``(o, o_var)`` in place of ``o``."""
     from .ops.palimpsa import _core
     _core._require_cuda(q, k, v, b, gt, g, Ip)
     if scale is None:
@@ -263,6 +281,17 @@ def cp_chunk_palimpsa(q, k, v, b, gt, g, Ip, group=None, scale=None, output_fina
     B, T, H, K = q.shape
     if num_segments is None:
         num_segments = _core.plan_segments(B, T, H, K, v.shape[-1])
-    o, fmu, fI = _CpChunkPalimpsa.apply(q, k, v, b, gt, g, Ip, float(scale), group, int(num_segments),
-                                        bool(reduce_param_grads))
-    return (o, fmu, fI) if output_final_state else o
+    if (initial_mu_state is None) != (initial_I_state is None):
+        raise ValueError("pass both initial_mu_state and initial_I_state, or neither")
+    if initial_mu_state is not None:
+        _core._require_cuda(initial_mu_state, initial_I_state)
+        shape = (B, H, v.shape[-1], K)
+        if tuple(initial_mu_state.shape) != shape or tuple(initial_I_state.shape) != shape:
+            raise ValueError(f"initial states must have shape {shape}")
+        initial_mu_state = initial_mu_state.detach().float().contiguous()
+        initial_I_state = initial_I_state.detach().float().contiguous()
+    o, o_var, fmu, fI = _CpChunkPalimpsa.apply(q, k, v, b, gt, g, Ip, float(scale), group, int(num_segments),
+                                               bool(reduce_param_grads), initial_mu_state, initial_I_state,
+                                               bool(output_uncertainty))
+    out = (o, o_var) if output_uncertainty else o
+    return (out, fmu, fI) if output_final_state else out

@@ -19,7 +19,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, q_out, dtype_name, T, G):
+def _worker(rank, world, port, q_out, dtype_name, T, G, extras=False):
     try:
         sys.path.insert(0, ROOT)
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -37,16 +37,32 @@ def _worker(rank, world, port, q_out, dtype_name, T, G):
         inp["gt"] = inp["gt"] * 0.05
         names = ("q", "k", "v", "b", "gt", "g", "Ip")
         full = {n: inp[n].to(dev).requires_grad_(True) for n in names}
-        o_ref, mu_ref, I_ref = chunk_palimpsa(*[full[n] for n in names], output_final_state=True)
-        o_ref.backward(inp["do"].to(dev))
+        kw = {}
+        if extras:      # explicit initial state (used on the first rank only) and the uncertainty output
+            mu0, I0 = orc.make_states(9, 2, 3, 48, 64, inp["Ip"])
+            kw = dict(initial_mu_state=mu0.to(dev), initial_I_state=I0.to(dev), output_uncertainty=True)
+        o_ref, mu_ref, I_ref = chunk_palimpsa(*[full[n] for n in names], output_final_state=True, **kw)
+        if extras:
+            o_ref, ov_ref = o_ref
+            (o_ref.float() * inp["do"].to(dev).float()).sum().add((ov_ref.float() * inp["do_var"].to(dev).float()).sum()
+                                                                  ).backward()
+        else:
+            o_ref.backward(inp["do"].to(dev))
         lo, hi = shard_bounds(T, rank, world)
         loc = {n: (inp[n][:, lo:hi] if inp[n].dim() >= 3 else inp[n]).to(dev).contiguous().requires_grad_(True)
                for n in names}
-        o, mu, I = cp_chunk_palimpsa(*[loc[n] for n in names], output_final_state=True, num_segments=G)
-        o.backward(inp["do"][:, lo:hi].to(dev))
+        o, mu, I = cp_chunk_palimpsa(*[loc[n] for n in names], output_final_state=True, num_segments=G, **kw)
+        if extras:
+            o, ov = o
+            (o.float() * inp["do"][:, lo:hi].to(dev).float()).sum().add(
+                (ov.float() * inp["do_var"][:, lo:hi].to(dev).float()).sum()).backward()
+        else:
+            o.backward(inp["do"][:, lo:hi].to(dev))
         torch.cuda.synchronize()
         tol = 1e-5 if dtype == torch.float32 else 2e-2
         errs = {"o": orc.rel_err(o, o_ref[:, lo:hi])}
+        if extras:
+            errs["o_var"] = orc.rel_err(ov, ov_ref[:, lo:hi])
         for n in ("q", "k", "v", "b", "gt"):
             errs["d" + n] = orc.rel_err(loc[n].grad, full[n].grad[:, lo:hi])
         for n in ("g", "Ip"):
@@ -62,8 +78,10 @@ def _worker(rank, world, port, q_out, dtype_name, T, G):
         q_out.put((rank, "error", traceback.format_exc()))
 
 
-@pytest.mark.parametrize("dtype_name,T,G", [("float32", 300, 1), ("float32", 333, 3), ("bfloat16", 1024, 2)])
-def test_cp_matches_single_gpu(dtype_name, T, G):
+@pytest.mark.parametrize("dtype_name,T,G,extras", [("float32", 300, 1, False), ("float32", 333, 3, False),
+                                                   ("bfloat16", 1024, 2, False), ("float32", 333, 2, True),
+                                                   ("bfloat16", 512, 2, True)])
+def test_cp_matches_single_gpu(dtype_name, T, G, extras):
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least 2 GPUs")
@@ -71,7 +89,7 @@ def test_cp_matches_single_gpu(dtype_name, T, G):
     ctx = mp.get_context("spawn")
     q_out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q_out, dtype_name, T, G)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q_out, dtype_name, T, G, extras)) for r in range(world)]
     for p in procs:
         p.start()
     got = [q_out.get(timeout=300) for _ in range(world)]
