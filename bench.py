@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the Palimpsa operator hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|decode|layer]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|decode|layer|varlen]
 
 Workload (default ``c2``): the 170M-model-shaped layer op, chunked forward + backward in bf16 with
 fp32 state, B=8, T=4096, H=6, d_k=d_v=128, seeded synthetic inputs (q,k L2-normalised N(0,1);
@@ -415,6 +415,47 @@ def run_decode(args):
                       "state_finite": bool(torch.isfinite(mu).all() and torch.isfinite(I).all())}), flush=True)
 
 
+def run_varlen(args):
+    """Extra workload (not the headline): one packed batch of 32 768 tokens made of documents with seeded
+    random lengths in [128, 4096] (H=6, d_k=d_v=128, bf16; states reset at every document boundary through
+    ``cu_seqlens``), forward + backward.  The shape of a packed-sequence training step.  Prints its own JSON line."""
+    from palimpsa_b200 import _lib
+    from palimpsa_b200.ops import chunk_palimpsa
+    _lib.lib()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    T, H, K, V = 32768, C2["H"], C2["K"], C2["V"]
+    gen = torch.Generator().manual_seed(0)
+    lens, tot = [], 0
+    while tot < T:
+        n = min(int(torch.randint(128, 4097, (1,), generator=gen).item()), T - tot)
+        lens.append(n)
+        tot += n
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+    _, d = make_inputs(1, T, H, K, V, torch.bfloat16, dev, seed=0)
+
+    def step():
+        leaves = [d[n].detach().requires_grad_(True) for n in ("q", "k", "v", "b", "gt", "g", "Ip")]
+        chunk_palimpsa(*leaves, cu_seqlens=cu).backward(d["do"])
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"metric": "fwd+bwd tokens/s (chunk, bf16, packed variable-length batch)", "value": T / (ms * 1e-3),
+                      "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+                      "ms_per_step": ms, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+                      "gpu_launches": 4 * args.steps,
+                      "config": {"workload": f"packed batch of {len(lens)} documents, {T} tokens, lengths {min(lens)}..{max(lens)}, "
+                                             f"H={H} d_k={K} d_v={V} bf16", "l2": "inputs 241 MiB > L2"}}), flush=True)
+
+
 def run_layer(args):
     """Extra workload (not the headline): the layer's element-wise prologue and epilogue around the operator on
     the C2 shapes (B=8 T=4096 H=6 d_k=d_v=128, bf16), forward and backward, as four fused kernels.  Each is
@@ -535,9 +576,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c2", "decode", "layer"],
+    ap.add_argument("--workload", default="c2", choices=["c2", "decode", "layer", "varlen"],
                     help="c2 (default, the headline), decode (extra line for the decode configuration) or layer "
-                         "(extra line for the fused element-wise kernels around the operator)")
+                         "(extra line for the fused element-wise kernels around the operator) or varlen (extra line "
+                         "for a packed variable-length batch)")
     ap.add_argument("--decode-steps", type=int, default=1000)
     ap.add_argument("--profile-batch", type=int, default=4, help="batch size of --profile-case")
     ap.add_argument("--profile-segments", type=int, default=1,
@@ -571,9 +613,9 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
-    if args.workload == "layer":
+    if args.workload in ("layer", "varlen"):
         if rank == 0:
-            run_layer(args)
+            (run_layer if args.workload == "layer" else run_varlen)(args)
         return
     if args.workload == "decode":
         if rank == 0:

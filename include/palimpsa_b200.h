@@ -135,8 +135,10 @@ typedef struct palimpsa_segments {
 /* Fills sum_M, sum_J and decay for every segment (no reciprocal, no output: the cheap pass). */
 int palimpsa_segment_summary(const palimpsa_problem *p, const palimpsa_segments *segs, void *cuda_stream);
 
-/* Diagnostic: 0 unless a bounded wait inside the tensor-core summary kernel (bf16 inputs: tcgen05 MMAs
- * into TMEM) ever gave up on this device; then the code of the wait.  Synchronises the device. */
+/* Diagnostic: 0 unless a bounded wait inside a kernel ever gave up on this device; then the code of the
+ * wait (1, 2: tensor-core summary kernel; 3, 4: tensor-core carried-gradient kernel; 5, 6: barriers of the
+ * backward main kernel).  Every in-kernel wait of this library is bounded: a kernel that gives up records
+ * the code, releases what it holds and returns, and its results are then invalid.  Synchronises the device. */
 int palimpsa_tensor_core_status(void);
 
 /* Forward boundary scan: start_M/start_I of every segment from the summaries.  The state before

@@ -149,8 +149,9 @@ int palimpsa_segment_summary(const palimpsa_problem* p, const palimpsa_segments*
 }
 
 int palimpsa_tensor_core_status(void) {
-    const int s = summary_tc_status();
-    return s ? s : carry_tc_status();
+    int s = summary_tc_status();
+    if (!s) s = carry_tc_status();
+    return s ? s : bwd_wait_status();
 }
 
 int palimpsa_carry_apply_supported(const palimpsa_problem* p) { return p && carry_tc_supported(*p) ? 1 : 0; }

@@ -23,12 +23,22 @@
 #include <cstdlib>
 #include <mutex>
 
-#include "common.cuh"
 #include "host.h"
+#include "tc_common.cuh"
 
 namespace palimpsa {
 
 constexpr int GR = 4;  // tokens per register-resident group
+
+// 0 ok; 5 / 6: a bounded wait on the split-phase barriers of the backward's group reduction gave up
+__device__ int g_bwd_status = 0;
+
+__device__ __forceinline__ void mbar_init_n(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tc::smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("{\n.reg .b64 st;\nmbarrier.arrive.shared::cta.b64 st, [%0];\n}" ::"r"(tc::smem_u32(bar)) : "memory");
+}
 
 struct BwdArgs {
     palimpsa_problem p;
@@ -285,6 +295,26 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
     const bool has_carry = !CO && a.carry_M != nullptr;
     const bool has_init = p.init_mu != nullptr || (p.flags & PALIMPSA_FLAG_EXPLICIT_INIT);
 
+    // With a single buffer for the d_k-indexed partials the two CTA-wide barriers per token group are split
+    // into arrive / wait halves (mbarriers, one arrival per warp): a warp that has written its partials goes
+    // on with its own shuffle reductions before it waits for the others' (A), and a warp that has read the
+    // buffer goes on with the next group's recompute before it waits for the others to finish reading (B).
+    // The warps of the CTA then drift apart by up to half a group and stop hitting the FP32 pipe and the
+    // reduction phases all at the same time.  Waits are bounded; a wait that gives up is recorded.
+    constexpr bool SPLIT = KBUF == 1 && !CO;
+    __shared__ __align__(8) unsigned long long gbar[2];
+    unsigned ph_a = 0, ph_b = 0;
+    int wait_fail = 0;
+    if (SPLIT) {
+        if (tid == 0) {
+            mbar_init_n(&gbar[0], W);
+            mbar_init_n(&gbar[1], W);
+            tc::mbar_init_fence();
+        }
+        __syncthreads();
+        if (lane == 0) mbar_arrive(&gbar[1]);  // nobody reads the buffer before the first group: B starts complete
+    }
+
     // this thread's d_k columns are RK*kg .. RK*kg+RK-1: pair q covers columns RK*kg + 2q, +1
     const float2* ks2 = reinterpret_cast<const float2*>(sm + L.ks) + NP * kg;
     const float2* qs2 = reinterpret_cast<const float2*>(sm + L.qs) + NP * kg;
@@ -525,6 +555,10 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                     red1[(j * RV + r) * 2 + 1] = -(dba.x + dba.y);
                 }
                 // this row group's share of dq and dk for the token -> shared memory
+                if (SPLIT && j == GR - 1) {  // first write of the group: the previous group's readers must be done
+                    if (!wait_fail && !tc::mbar_wait(&gbar[1], ph_b)) wait_fail = 6;  // after one failure: no more waiting
+                    ph_b ^= 1;
+                }
                 if (!CO) {
                     float2* dst = kred2 + (gi & (KBUF - 1)) * (GR * WV * 2 * KP2) + ((j * WV + wv) * 2) * KP2 + NP * kg;
                     const float2 sc2 = dup2(p.scale), m2 = dup2(-2.f);
@@ -548,6 +582,10 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                 red2[j * 2 + 1] = -sc_;
             }
             if (CO) continue;  // carry-only pass: nothing but the state gradients is wanted
+            if (SPLIT) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&gbar[0]);  // this warp's partials of the group are written
+            }
             // d_v-indexed sums over the KG lanes of a row; per-token scalars over the whole warp
             xreduce<NR1, KG>(red1, lane);
             {
@@ -568,7 +606,12 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                 const int id = xreduce_index<NR2, 32>(lane);
                 wred[(w * TB + gi * GR + (id >> 1)) * 2 + (id & 1)] = red2[0];
             }
-            __syncthreads();
+            if (SPLIT) {
+                if (!wait_fail && !tc::mbar_wait(&gbar[0], ph_a)) wait_fail = 5;
+                ph_a ^= 1;
+            } else {
+                __syncthreads();
+            }
             // ---- sum the row groups' shares; emit this row tile's dq / dk partials ----------------------
             const int ng = min(GR, nt - gi * GR);  // tokens of the group that exist (<= 0 past the sequence end)
             for (int i = tid; i < ng * KP2; i += NTHR) {
@@ -586,7 +629,10 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
             }
             // with two buffers no second barrier is needed: the next group writes the other buffer, and the
             // barrier after ITS reverse walk orders this group's reads before the buffer is reused
-            if (KBUF == 1) __syncthreads();
+            if (SPLIT) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&gbar[1]);  // this warp has read the buffer
+            }
         }
         if (!CO) __syncthreads();  // dvs / dbs / wred of the whole block are complete
 
@@ -616,6 +662,8 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
         }
         // the next iteration's first barrier orders these reads before the buffers are reused
     }
+
+    if (SPLIT && wait_fail) atomicCAS(&g_bwd_status, 0, wait_fail);
 
     // ---- gradient w.r.t. the segment's start state: decay the first token's totals once more ----------
     if (a.rloc_M) {
@@ -813,6 +861,13 @@ static int launch_bwd_t(const BwdArgs& a, int tiles, int num_seg, bool carry_onl
         if (cfg.W == 12) return launch_bwd_w<RK, KG, RV, 12>(a, tiles, num_seg, carry_only, stream);
     if constexpr (RV > 1) return launch_bwd_w<RK, KG, RV, 4>(a, tiles, num_seg, carry_only, stream);
     return PALIMPSA_E_DIM;
+}
+
+int bwd_wait_status() {
+    int s = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(&s, g_bwd_status, sizeof(int)) != cudaSuccess) return -1;
+    return s;
 }
 
 static bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }

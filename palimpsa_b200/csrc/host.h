@@ -30,6 +30,7 @@ int summary_tc_status();
 bool carry_tc_supported(const palimpsa_problem& p);
 int launch_carry_tc(const palimpsa_bwd_params* prm, const palimpsa_segments& segs, cudaStream_t stream);
 int carry_tc_status();
+int bwd_wait_status();  // 0, or the code of a bounded barrier wait of the backward main kernel that gave up
 
 // Boundary scans over segments (segments.cu).
 int launch_combine_fwd(const palimpsa_problem& p, const palimpsa_segments& segs, const float* in_M, const float* in_J,
