@@ -683,43 +683,71 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
 }
 
 // ---- finishing kernel 1: one warp per (token, head) row ------------------------------------------------
-__global__ void bwd_finish_rows(const palimpsa_problem p, const float* __restrict__ dq_part,
-                                const float* __restrict__ dk_part, const float* __restrict__ df_part,
-                                const float* __restrict__ dip_part, void* dq, void* dk, float* dgt, float* w_dg,
-                                float* w_dip, int tiles, int tiles_k, int KP, long long rows) {
+__device__ __forceinline__ void st2(void* base, long long idx, float2 x, int dt) {  // idx even, base 8-byte aligned
+    if (dt == PALIMPSA_F32)
+        *reinterpret_cast<float2*>(reinterpret_cast<float*>(base) + idx) = x;
+    else if (dt == PALIMPSA_BF16)
+        *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(base) + idx) = __floats2bfloat162_rn(x.x, x.y);
+    else
+        *reinterpret_cast<__half2*>(reinterpret_cast<__half*>(base) + idx) = __floats2half2_rn(x.x, x.y);
+}
+
+__global__ void __launch_bounds__(256) bwd_finish_rows(const palimpsa_problem p, const float* __restrict__ dq_part,
+                                                       const float* __restrict__ dk_part,
+                                                       const float* __restrict__ df_part,
+                                                       const float* __restrict__ dip_part, void* dq, void* dk,
+                                                       float* dgt, float* w_dg, float* w_dip, int tiles, int tiles_k,
+                                                       int KP, long long rows, int pairs_ok) {
     const int lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
     const int h = (int)(row % p.H);
     const int KP2 = KP / 2;
+    // per-token scalars: lane t fetches tile t's partial (tiles beyond 32 go round), summed by a fixed butterfly
+    float df = 0.f, dip = 0.f;
+    for (int t = lane; t < tiles_k; t += 32) {
+        df += df_part[(size_t)t * rows + row];
+        dip += dip_part[(size_t)t * rows + row];
+    }
+    const float gtv = p.gt[row], gh = p.g[h];
     for (int pi = lane; pi < KP2; pi += 32) {
         float2 sq = make_float2(0.f, 0.f), sk = sq;
-        for (int t = 0; t < tiles_k; ++t) {  // dk may have one slot more than dq: the carried-gradient terms
-            const size_t e = ((size_t)t * rows + row) * KP2 + pi;
-            if (t < tiles) {
-                const float2 x = reinterpret_cast<const float2*>(dq_part)[e];
-                sq.x += x.x, sq.y += x.y;
-            }
-            const float2 y = reinterpret_cast<const float2*>(dk_part)[e];
+        const float2* pq = reinterpret_cast<const float2*>(dq_part) + (size_t)row * KP2 + pi;
+        const float2* pk = reinterpret_cast<const float2*>(dk_part) + (size_t)row * KP2 + pi;
+        const size_t step = (size_t)rows * KP2;
+#pragma unroll 4
+        for (int t = 0; t < tiles; ++t) {
+            const float2 x = pq[t * step], y = pk[t * step];
+            sq.x += x.x, sq.y += x.y;
+            sk.x += y.x, sk.y += y.y;
+        }
+        if (tiles_k > tiles) {  // dk has one slot more than dq: the carried-gradient terms
+            const float2 y = pk[tiles * step];
             sk.x += y.x, sk.y += y.y;
         }
         const int kc = 2 * pi;
-        if (kc < p.K) {
-            st1(dq, row * p.K + kc, sq.x, p.io_dtype);
-            st1(dk, row * p.K + kc, sk.x, p.io_dtype);
-        }
-        if (kc + 1 < p.K) {
-            st1(dq, row * p.K + kc + 1, sq.y, p.io_dtype);
-            st1(dk, row * p.K + kc + 1, sk.y, p.io_dtype);
+        if (pairs_ok) {
+            if (kc < p.K) {
+                st2(dq, row * p.K + kc, sq, p.io_dtype);
+                st2(dk, row * p.K + kc, sk, p.io_dtype);
+            }
+        } else {
+            if (kc < p.K) {
+                st1(dq, row * p.K + kc, sq.x, p.io_dtype);
+                st1(dk, row * p.K + kc, sk.x, p.io_dtype);
+            }
+            if (kc + 1 < p.K) {
+                st1(dq, row * p.K + kc + 1, sq.y, p.io_dtype);
+                st1(dk, row * p.K + kc + 1, sk.y, p.io_dtype);
+            }
         }
     }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        df += __shfl_xor_sync(0xffffffffu, df, off);
+        dip += __shfl_xor_sync(0xffffffffu, dip, off);
+    }
     if (lane == 0) {
-        float df = 0.f, dip = 0.f;
-        for (int t = 0; t < tiles_k; ++t) {
-            df += df_part[(size_t)t * rows + row];
-            dip += dip_part[(size_t)t * rows + row];
-        }
-        const float gtv = p.gt[row], gh = p.g[h];
         const float f = expf(-gtv * gh);
         dgt[row] = -gh * f * df;
         w_dg[row] = -gtv * f * df;
@@ -925,7 +953,8 @@ int launch_bwd(const palimpsa_bwd_params* prm, const palimpsa_segments* segs, bo
         bwd_finish_rows<<<(unsigned)((rows + wpb - 1) / wpb), 32 * wpb, 0, stream>>>(
             p, a.dq_part, a.dk_part, a.df_part, a.dip_part, prm->dq, prm->dk, prm->dgt,
             reinterpret_cast<float*>(base + ws.w_dg), reinterpret_cast<float*>(base + ws.w_dip), ws.tiles,
-            ws.tiles + ((stages & 4) ? 1 : 0), ws.KP, rows);
+            ws.tiles + ((stages & 4) ? 1 : 0), ws.KP, rows,
+            (p.K % 2 == 0 && ((reinterpret_cast<uintptr_t>(prm->dq) | reinterpret_cast<uintptr_t>(prm->dk)) & 7) == 0) ? 1 : 0);
         if (cudaGetLastError() != cudaSuccess) return PALIMPSA_E_LAUNCH;
     }
     bwd_finish_heads<<<p.H, 256, 0, stream>>>(reinterpret_cast<float*>(base + ws.w_dg),

@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(256, min_ctas(NCK * NCV, 4)) layer_prologue_fw
 // y = x / n, n = max(|x|, eps):  dx = (G - y <y, G>) / n  (G = sum of the gradients of the repeated heads;
 // with the norm clamped, n is a constant and dx = G / eps).
 template <int DT, int NCK, int NCV, bool VECK, bool VECV>
-__global__ void __launch_bounds__(256, min_ctas(NCK * NCV, 3)) layer_prologue_bwd_kernel(const palimpsa_layer_prologue a, int qrows,
+__global__ void __launch_bounds__(256, min_ctas(NCK * NCV, 4)) layer_prologue_bwd_kernel(const palimpsa_layer_prologue a, int qrows,
                                                                     float* w_dtb, float* w_bsc) {
     extern __shared__ float head_tab[];  // [2][H]: softplus(b_scale), its derivative
     const int lane = threadIdx.x & 31;
@@ -304,13 +304,8 @@ __global__ void __launch_bounds__(256, min_ctas(NCK * NCV, 3)) layer_prologue_bw
 // out[h] = sum over tokens of w[token*H + h] in a fixed order, for up to two arrays at once (blockIdx.y picks
 // the array): one CTA of 1024 threads per head; every thread sums a strided subsequence with 8 loads in
 // flight, then a tree over the CTA.
-__global__ void __launch_bounds__(1024) layer_sum_heads_kernel(const float* __restrict__ w0, float* __restrict__ out0,
-                                                               const float* __restrict__ w1, float* __restrict__ out1,
-                                                               long long tokens, int H) {
-    __shared__ float red[1024];
-    const float* __restrict__ w = blockIdx.y ? w1 : w0;
-    float* __restrict__ out = blockIdx.y ? out1 : out0;
-    const int h = blockIdx.x;
+__device__ __forceinline__ void sum_heads_body(const float* __restrict__ w, float* __restrict__ out, long long tokens,
+                                               int H, int h, float* red) {
     float s = 0.f;
     long long t = threadIdx.x;
     for (; t + 7 * 1024 < tokens; t += 8 * 1024) {
@@ -328,6 +323,12 @@ __global__ void __launch_bounds__(1024) layer_sum_heads_kernel(const float* __re
         __syncthreads();
     }
     if (threadIdx.x == 0) out[h] = red[0];
+}
+__global__ void __launch_bounds__(1024) layer_sum_heads_kernel(const float* __restrict__ w0, float* __restrict__ out0,
+                                                               const float* __restrict__ w1, float* __restrict__ out1,
+                                                               long long tokens, int H) {
+    __shared__ float red[1024];
+    sum_heads_body(blockIdx.y ? w1 : w0, blockIdx.y ? out1 : out0, tokens, H, blockIdx.x, red);
 }
 
 // ---- epilogue, forward -----------------------------------------------------------------------------------
@@ -388,7 +389,7 @@ __global__ void __launch_bounds__(256, min_ctas(NC, 4)) layer_epilogue_fwd_kerne
 //   xh = z r,  yn = xh w,  y = yn g s(g):   dg = dy yn (s + g s (1-s)),  dyn = dy g s(g)  (or dy without gate)
 //   dw += dyn xh,  dxh = dyn w,  dz = r (dxh - xh mean(dxh xh)),  d_o = dz,  dx = dz D,  dD += <dz, x>
 template <int DT, int NC, int R, bool VEC>
-__global__ void __launch_bounds__(256, min_ctas(NC, 3)) layer_epilogue_bwd_kernel(const palimpsa_layer_epilogue a, int rows,
+__global__ void __launch_bounds__(256, min_ctas(NC, 4)) layer_epilogue_bwd_kernel(const palimpsa_layer_epilogue a, int rows,
                                                                     float* w_dD, float* w_dw) {
     __shared__ float4 red[8][32];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -493,11 +494,10 @@ __global__ void __launch_bounds__(256, min_ctas(NC, 3)) layer_epilogue_bwd_kerne
 
 // out[v] = sum over partial rows of w[r*V + v] in a fixed order: a CTA covers 32 columns with 32 row slices
 // (every thread sums rows slice, slice+32, ... with 8 loads in flight), then the slices are summed in order.
-__global__ void __launch_bounds__(1024) layer_sum_cols_kernel(const float* __restrict__ w, float* __restrict__ out,
-                                                              int nrows, int V) {
-    __shared__ float red[32][33];
+__device__ __forceinline__ void sum_cols_body(const float* __restrict__ w, float* __restrict__ out, int nrows, int V,
+                                              int cblock, float* red) {
     const int cx = threadIdx.x & 31, sl = threadIdx.x >> 5;
-    const int v = blockIdx.x * 32 + cx;
+    const int v = cblock * 32 + cx;
     float s = 0.f;
     if (v < V) {
         int r = sl;
@@ -510,13 +510,25 @@ __global__ void __launch_bounds__(1024) layer_sum_cols_kernel(const float* __res
         }
         for (; r < nrows; r += 32) s += w[(long long)r * V + v];
     }
-    red[sl][cx] = s;
+    red[sl * 32 + cx] = s;
     __syncthreads();
     if (sl == 0 && v < V) {
         float t = 0.f;
-        for (int i = 0; i < 32; ++i) t += red[i][cx];
+        for (int i = 0; i < 32; ++i) t += red[i * 32 + cx];
         out[v] = t;
     }
+}
+// The epilogue backward's two parameter reductions in one launch: CTAs [0, nh) sum dD per head (nh = H, or 0
+// without the residual), the others sum 32 columns of dweight each.
+__global__ void __launch_bounds__(1024) layer_epilogue_reduce_kernel(const float* __restrict__ w_dD,
+                                                                     float* __restrict__ dD, long long tokens, int H,
+                                                                     int nh, const float* __restrict__ w_dw,
+                                                                     float* __restrict__ dweight, int nrows, int V) {
+    __shared__ float red[1024];
+    if ((int)blockIdx.x < nh)
+        sum_heads_body(w_dD, dD, tokens, H, blockIdx.x, red);
+    else
+        sum_cols_body(w_dw, dweight, nrows, V, blockIdx.x - nh, red);
 }
 
 }  // namespace
@@ -786,8 +798,9 @@ int palimpsa_layer_epilogue_bwd(const palimpsa_layer_epilogue* a, void* cuda_str
 #undef CALL_V
         if (int rc = launched()) return rc;
     }
-    if (res) layer_sum_heads_kernel<<<dim3(a->H, 1), 1024, 0, st>>>(w_dD, a->dD, w_dD, a->dD, a->tokens, a->H);
-    layer_sum_cols_kernel<<<(a->V + 31) / 32, 1024, 0, st>>>(w_dw, a->dweight, (int)nb, a->V);
+    const int nh = res ? a->H : 0;
+    layer_epilogue_reduce_kernel<<<nh + (a->V + 31) / 32, 1024, 0, st>>>(w_dD, a->dD, a->tokens, a->H, nh, w_dw,
+                                                                          a->dweight, (int)nb, a->V);
     return launched();
 }
 
