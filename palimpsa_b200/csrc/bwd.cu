@@ -69,6 +69,10 @@ struct BwdSmem {
 // the shared memory allows it, i.e. up to 8 warps and d_k <= 128.
 __host__ __device__ constexpr int bwd_kred_buffers(int nthr, int KP) { return (nthr > 256 || KP > 128) ? 1 : 2; }
 
+// Columns per token of the raw d_v-indexed staging tiles: the row tile widened to 16-byte boundaries of the
+// global rows on both sides (a tile of 22 rows does not start on one).
+__host__ __device__ constexpr int bwd_staged_cols(int TV) { return (TV + 7) / 8 * 8 + 8; }
+
 // Shared-memory plan of one backward CTA (KP padded d_k, TV state rows, NE state elements per thread,
 // WV row groups).  Operand tiles v, b, dy are stored with every value duplicated ({x, x}) so that a
 // 64-bit load yields the register pair the packed FP32 instructions want.
@@ -103,12 +107,13 @@ __host__ __device__ inline BwdSmem bwd_smem_layout(int KP, int TV, int NE, int n
         r += round_up(bytes, 16);
         return o;
     };
+    const int TVS = bwd_staged_cols(TV);
     s.rq = rtake(TB * KP * es);
     s.rk = rtake(TB * KP * es);
-    s.rv = rtake(TB * TV * es);
-    s.rb = rtake(TB * TV * es);
-    s.rdo = rtake(TB * TV * es);
-    s.rdov = unc ? rtake(TB * TV * es) : 0;
+    s.rv = rtake(TB * TVS * es);
+    s.rb = rtake(TB * TVS * es);
+    s.rdo = rtake(TB * TVS * es);
+    s.rdov = unc ? rtake(TB * TVS * es) : 0;
     s.rgt = rtake((TB + 1) * 4);
     s.total = off + r;
     return s;
@@ -144,21 +149,32 @@ __device__ __forceinline__ void bwd_issue_raw(const BwdArgs& a, unsigned char* s
         cp_async16(stage + L.rq + dst, gq + src);
         cp_async16(stage + L.rk + dst, gk + src);
     }
-    const int cv = tvw * es / 16;
+    // the aligned superset [va, va + span) of the tile's columns [v0, v0 + tvw); d_v*es is a multiple of 16 on
+    // this path, so the superset stays inside the row
+    const int ea = 16 / es, va = v0 / ea * ea, span = (v0 - va + tvw + ea - 1) / ea * ea;
+    const int cv = span * es / 16, TVS = bwd_staged_cols(TV);
     const char* gv = reinterpret_cast<const char*>(p.v);
     const char* gb = reinterpret_cast<const char*>(p.b);
     const char* gdo = reinterpret_cast<const char*>(a.d_o);
     const char* gdov = reinterpret_cast<const char*>(a.d_o_var);
     for (int i = tid; i < nt * cv; i += nthr) {
         int t = i / cv, c = i - t * cv;
-        long long src = (((tok0 + t) * p.H + h) * (long long)p.V + v0) * es + c * 16;
-        int dst = t * TV * es + c * 16;
+        long long src = (((tok0 + t) * p.H + h) * (long long)p.V + va) * es + c * 16;
+        int dst = t * TVS * es + c * 16;
         cp_async16(stage + L.rv + dst, gv + src);
         cp_async16(stage + L.rb + dst, gb + src);
         cp_async16(stage + L.rdo + dst, gdo + src);
         if (gdov) cp_async16(stage + L.rdov + dst, gdov + src);
     }
     for (int i = tid; i < nt_ext; i += nthr) cp_async4(stage + L.rgt + i * 4, p.gt + (tok0 + i) * p.H + h);
+}
+
+// Two consecutive staged values starting at the even element index e (shared memory).
+template <int DT>
+__device__ __forceinline__ float2 ld2s(const unsigned char* base, int e) {
+    if (DT == PALIMPSA_F32) return *reinterpret_cast<const float2*>(base + (size_t)e * 4);
+    if (DT == PALIMPSA_BF16) return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(base + (size_t)e * 2));
+    return __half22float2(*reinterpret_cast<const __half2*>(base + (size_t)e * 2));
 }
 
 template <int DT, bool ALIGNED, bool UNC>
@@ -194,15 +210,46 @@ __device__ __forceinline__ void bwd_convert(const BwdArgs& a, unsigned char* sm,
     float4* bs = reinterpret_cast<float4*>(sm + L.bs2);
     float4* dys = reinterpret_cast<float4*>(sm + L.dys2);
     float4* dyvs = reinterpret_cast<float4*>(sm + L.dyvs2);
+    const int TVS = bwd_staged_cols(TV);
+    const int voff = ALIGNED ? v0 % (16 / dtype_size(DT)) : 0;  // tile start inside the staged superset
+    if ((TV | voff) & 3) {
+        // tile width or offset not a multiple of 4 (both are even): two values at a time
+        const int V2 = TV / 2;
+        for (int i = tid; i < TB * V2; i += nthr) {
+            const int t = i / V2, c2 = i - t * V2;
+            float2 vv = make_float2(0.f, 0.f), bv = vv, dv = vv, dvv = vv;
+            if (t < nt && v0 + c2 * 2 < p.V) {
+                if (ALIGNED) {
+                    const int e = t * TVS + voff + 2 * c2;
+                    vv = ld2s<DT>(stage + L.rv, e);
+                    bv = ld2s<DT>(stage + L.rb, e);
+                    dv = ld2s<DT>(stage + L.rdo, e);
+                    if (UNC) dvv = ld2s<DT>(stage + L.rdov, e);
+                } else {
+                    const long long row = ((tok0 + t) * p.H + h) * (long long)p.V, e = row + v0 + c2 * 2;
+                    const bool two = e + 1 < row + p.V;
+                    vv = make_float2(ld1<DT>(p.v, e), two ? ld1<DT>(p.v, e + 1) : 0.f);
+                    bv = make_float2(ld1<DT>(p.b, e), two ? ld1<DT>(p.b, e + 1) : 0.f);
+                    dv = make_float2(ld1<DT>(a.d_o, e), two ? ld1<DT>(a.d_o, e + 1) : 0.f);
+                    if (UNC) dvv = make_float2(ld1<DT>(a.d_o_var, e), two ? ld1<DT>(a.d_o_var, e + 1) : 0.f);
+                }
+            }
+            vs[i] = make_float4(vv.x, vv.x, vv.y, vv.y);
+            bs[i] = make_float4(bv.x, bv.x, bv.y, bv.y);
+            dys[i] = make_float4(dv.x, dv.x, dv.y, dv.y);
+            if (UNC) dyvs[i] = make_float4(dvv.x, dvv.x, dvv.y, dvv.y);
+        }
+    } else
     for (int i = tid; i < TB * V4; i += nthr) {
         int t = i / V4, c4 = i - t * V4;
         float4 vv = make_float4(0.f, 0.f, 0.f, 0.f), bv = vv, dv = vv, dvv = vv;
         if (t < nt && v0 + c4 * 4 < p.V) {
             if (ALIGNED) {
-                vv = ld4<DT>(stage + L.rv, i);
-                bv = ld4<DT>(stage + L.rb, i);
-                dv = ld4<DT>(stage + L.rdo, i);
-                if (UNC) dvv = ld4<DT>(stage + L.rdov, i);
+                const int g4 = (t * TVS + voff) / 4 + c4;  // TVS, voff multiples of 4 here
+                vv = ld4<DT>(stage + L.rv, g4);
+                bv = ld4<DT>(stage + L.rb, g4);
+                dv = ld4<DT>(stage + L.rdo, g4);
+                if (UNC) dvv = ld4<DT>(stage + L.rdov, g4);
             } else {
                 long long row = ((tok0 + t) * p.H + h) * (long long)p.V;
                 vv = ld4_guarded<DT>(p.v, row + v0 + c4 * 4, row + p.V);
@@ -815,13 +862,17 @@ static BwdConfig bwd_config(const palimpsa_problem& p) {
     int W = (rpw == 1 || p.V > 4 * rpw) ? 8 : 4;
     static const int force_w = [] { const char* e = getenv("PALIMPSA_BWD_WARPS"); return e ? atoi(e) : 0; }();
     if (force_w == 4 && rpw > 1) W = 4;
-    // d_k = 128: 12 warps (24 rows) per CTA hide latency better than 8 and give 2 even waves on 148 SMs
-    if (KP == 128 && rpw == 2 && p.V >= 48 && force_w != 8) W = 12;
+    // d_k = 128: 11 or 12 warps (22 / 24 rows) per CTA hide latency better than 8; of the two, the one that
+    // pads d_v with fewer idle rows (d_v = 128: 6 tiles of 22 rows = 132 instead of 144)
+    if (KP == 128 && rpw == 2 && p.V >= 48 && force_w != 8) {
+        const int pad11 = (p.V + 21) / 22 * 22, pad12 = (p.V + 23) / 24 * 24;
+        W = (pad11 < pad12 && force_w != 12) || force_w == 11 ? 11 : 12;
+    }
     for (;;) {
         c.W = W;
         c.TV = W * rpw;
         c.smem = bwd_smem_layout(KP, c.TV, c.s.RV * c.s.RK, 32 * W, W * VG, es, unc).total;
-        if (c.smem <= 227 * 1024 || W == 4 || rpw == 1 || W == 12) break;
+        if (c.smem <= 227 * 1024 || W == 4 || rpw == 1 || W >= 11) break;
         W = 4;
     }
     return c;
@@ -885,8 +936,10 @@ template <int RK, int KG, int RV>
 static int launch_bwd_t(const BwdArgs& a, int tiles, int num_seg, bool carry_only, cudaStream_t stream) {
     const BwdConfig cfg = bwd_config(a.p);
     if (cfg.W == 8) return launch_bwd_w<RK, KG, RV, 8>(a, tiles, num_seg, carry_only, stream);
-    if constexpr (RK == 4 && KG == 32 && RV == 2)
+    if constexpr (RK == 4 && KG == 32 && RV == 2) {
         if (cfg.W == 12) return launch_bwd_w<RK, KG, RV, 12>(a, tiles, num_seg, carry_only, stream);
+        if (cfg.W == 11) return launch_bwd_w<RK, KG, RV, 11>(a, tiles, num_seg, carry_only, stream);
+    }
     if constexpr (RV > 1) return launch_bwd_w<RK, KG, RV, 4>(a, tiles, num_seg, carry_only, stream);
     return PALIMPSA_E_DIM;
 }
