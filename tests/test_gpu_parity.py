@@ -60,6 +60,17 @@ def test_shipped_head_shapes(K, V, dtype):
     compare(got, ref, tol_for(dtype), what=f"K={K} V={V} {dtype}")
 
 
+@pytest.mark.parametrize("V", [64, 108, 128, 130, 136, 200])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_row_tiling_at_dk128(V, dtype):
+    """d_k = 128 picks 22- or 24-row tiles by padding; 22-row tiles start off the 16-byte grid of the rows
+    (staged supersets), and d_v that is not a multiple of 8 takes the unstaged path."""
+    inp = orc.make_inputs(V, B=2, T=50, H=2, K=128, V=V, dtype=dtype)
+    got = run_cuda(inp, "chunk", unc=True)
+    ref = run_oracle(inp, unc=True)
+    compare(got, ref, tol_for(dtype), what=f"K=128 V={V} {dtype}")
+
+
 @pytest.mark.parametrize("dtype,unc", [(torch.float32, False), (torch.float32, True), (torch.bfloat16, True)])
 def test_k256(dtype, unc):
     """The widest supported d_k: one state row per thread column group, 8-row tiles in the backward."""
