@@ -49,6 +49,7 @@ struct BwdArgs {
     float *dq_part, *dk_part, *df_part, *dip_part;
     void *dv, *db;
     int aligned;
+    int kbuf;        // shared-memory buffers for the per-group d_k-indexed partials: 2 where they fit, else 1
     int rows_total;  // tokens * H
     // segments (gridDim.z of them per sequence; seg_len tokens each, a multiple of 16; 0 = whole sequence)
     int seg_len;
@@ -65,10 +66,6 @@ struct BwdSmem {
     int total;
 };
 
-// Buffers for the d_k-indexed partials of a token group: two (one barrier per group instead of two) where
-// the shared memory allows it, i.e. up to 8 warps and d_k <= 128.
-__host__ __device__ constexpr int bwd_kred_buffers(int nthr, int KP) { return (nthr > 256 || KP > 128) ? 1 : 2; }
-
 // Columns per token of the raw d_v-indexed staging tiles: the row tile widened to 16-byte boundaries of the
 // global rows on both sides (a tile of 22 rows does not start on one).
 __host__ __device__ constexpr int bwd_staged_cols(int TV) { return (TV + 7) / 8 * 8 + 8; }
@@ -76,7 +73,8 @@ __host__ __device__ constexpr int bwd_staged_cols(int TV) { return (TV + 7) / 8 
 // Shared-memory plan of one backward CTA (KP padded d_k, TV state rows, NE state elements per thread,
 // WV row groups).  Operand tiles v, b, dy are stored with every value duplicated ({x, x}) so that a
 // 64-bit load yields the register pair the packed FP32 instructions want.
-__host__ __device__ inline BwdSmem bwd_smem_layout(int KP, int TV, int NE, int nthr, int WV, int es, bool unc) {
+__host__ __device__ inline BwdSmem bwd_smem_layout(int KP, int TV, int NE, int nthr, int WV, int es, bool unc,
+                                                  int kbuf) {
     BwdSmem s;
     int off = 0;
     auto take = [&](int bytes) {
@@ -99,7 +97,7 @@ __host__ __device__ inline BwdSmem bwd_smem_layout(int KP, int TV, int NE, int n
     s.slots = take(2 * 2 * NE * nthr * 4);
     s.ck_stage = 2 * TV * KP * 4;
     s.ckb = take(2 * s.ck_stage);
-    s.kred = take(bwd_kred_buffers(nthr, KP) * GR * WV * 2 * KP * 4);
+    s.kred = take(kbuf * GR * WV * 2 * KP * 4);  // kbuf = 2 group buffers where they fit (host's choice), else 1
     s.raw = off;
     int r = 0;
     auto rtake = [&](int bytes) {
@@ -298,7 +296,6 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
     constexpr int KP = RK * KG, VG = 32 / KG, NP = RK / 2, NE = RV * RK, KP2 = KP / 2;
     constexpr int TV = W * VG * RV, WV = W * VG, NTHR = 32 * W;
     constexpr int NG = TB / GR;       // groups per block
-    constexpr int KBUF = bwd_kred_buffers(NTHR, KP);  // shared-memory buffers for the d_k-indexed partials
     constexpr int NR1 = GR * RV * 2;  // per-group d_v-indexed partials of a thread: (token, row, dv|db)
     constexpr int NR2 = GR * 2;       // per-group per-token scalars: (token, df|sum GI)
     extern __shared__ __align__(16) unsigned char sm[];
@@ -311,7 +308,8 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
     const int v0 = tile * TV;
     const int tvw = min(TV, p.V - v0);
     const int es = dtype_size(p.io_dtype);
-    const BwdSmem L = bwd_smem_layout(KP, TV, NE, NTHR, WV, es, UNC);
+    const int KBUF = a.kbuf;  // shared-memory buffers for the d_k-indexed partials of a token group (1 or 2)
+    const BwdSmem L = bwd_smem_layout(KP, TV, NE, NTHR, WV, es, UNC, KBUF);
     int bos, len;
     seq_range(p, n, bos, len);
     // this CTA's segment of the sequence: tokens [s0, s1), blocks [blk0, blk1)
@@ -342,24 +340,26 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
     const bool has_carry = !CO && a.carry_M != nullptr;
     const bool has_init = p.init_mu != nullptr || (p.flags & PALIMPSA_FLAG_EXPLICIT_INIT);
 
-    // With a single buffer for the d_k-indexed partials the two CTA-wide barriers per token group are split
-    // into arrive / wait halves (mbarriers, one arrival per warp): a warp that has written its partials goes
-    // on with its own shuffle reductions before it waits for the others' (A), and a warp that has read the
-    // buffer goes on with the next group's recompute before it waits for the others to finish reading (B).
-    // The warps of the CTA then drift apart by up to half a group and stop hitting the FP32 pipe and the
-    // reduction phases all at the same time.  Waits are bounded; a wait that gives up is recorded.
-    constexpr bool SPLIT = KBUF == 1 && !CO;
+    // The CTA-wide barriers of the per-group reduction over d_v are split into arrive / wait halves
+    // (mbarriers, one arrival per warp).  A: a warp that has written its partials of a group goes on with its
+    // own shuffle reductions before it waits for the others' partials.  B (single buffer only): a warp that
+    // has read the buffer goes on with the next group's recompute before it waits for the others to finish
+    // reading; with two buffers the next group writes the other one and A alone orders everything.  The warps
+    // of the CTA then drift apart by up to a group and stop hitting the FP32 pipe and the reduction phases
+    // all at the same time.  Waits are bounded; a wait that gives up is recorded.
+    constexpr bool SPLIT_A = !CO;
+    const bool SPLIT_B = KBUF == 1 && !CO;
     __shared__ __align__(8) unsigned long long gbar[2];
     unsigned ph_a = 0, ph_b = 0;
     int wait_fail = 0;
-    if (SPLIT) {
+    if (SPLIT_A) {
         if (tid == 0) {
             mbar_init_n(&gbar[0], W);
             mbar_init_n(&gbar[1], W);
             tc::mbar_init_fence();
         }
         __syncthreads();
-        if (lane == 0) mbar_arrive(&gbar[1]);  // nobody reads the buffer before the first group: B starts complete
+        if (SPLIT_B && lane == 0) mbar_arrive(&gbar[1]);  // nobody reads before the first group: B starts complete
     }
 
     // this thread's d_k columns are RK*kg .. RK*kg+RK-1: pair q covers columns RK*kg + 2q, +1
@@ -602,7 +602,7 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                     red1[(j * RV + r) * 2 + 1] = -(dba.x + dba.y);
                 }
                 // this row group's share of dq and dk for the token -> shared memory
-                if (SPLIT && j == GR - 1) {  // first write of the group: the previous group's readers must be done
+                if (SPLIT_B && j == GR - 1) {  // first write of the group: the previous group's readers must be done
                     if (!wait_fail && !tc::mbar_wait(&gbar[1], ph_b)) wait_fail = 6;  // after one failure: no more waiting
                     ph_b ^= 1;
                 }
@@ -629,10 +629,8 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                 red2[j * 2 + 1] = -sc_;
             }
             if (CO) continue;  // carry-only pass: nothing but the state gradients is wanted
-            if (SPLIT) {
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&gbar[0]);  // this warp's partials of the group are written
-            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&gbar[0]);  // this warp's partials of the group are written
             // d_v-indexed sums over the KG lanes of a row; per-token scalars over the whole warp
             xreduce<NR1, KG>(red1, lane);
             {
@@ -653,12 +651,8 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                 const int id = xreduce_index<NR2, 32>(lane);
                 wred[(w * TB + gi * GR + (id >> 1)) * 2 + (id & 1)] = red2[0];
             }
-            if (SPLIT) {
-                if (!wait_fail && !tc::mbar_wait(&gbar[0], ph_a)) wait_fail = 5;
-                ph_a ^= 1;
-            } else {
-                __syncthreads();
-            }
+            if (!wait_fail && !tc::mbar_wait(&gbar[0], ph_a)) wait_fail = 5;
+            ph_a ^= 1;
             // ---- sum the row groups' shares; emit this row tile's dq / dk partials ----------------------
             const int ng = min(GR, nt - gi * GR);  // tokens of the group that exist (<= 0 past the sequence end)
             for (int i = tid; i < ng * KP2; i += NTHR) {
@@ -676,7 +670,7 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
             }
             // with two buffers no second barrier is needed: the next group writes the other buffer, and the
             // barrier after ITS reverse walk orders this group's reads before the buffer is reused
-            if (SPLIT) {
+            if (SPLIT_B) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&gbar[1]);  // this warp has read the buffer
             }
@@ -710,7 +704,7 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
         // the next iteration's first barrier orders these reads before the buffers are reused
     }
 
-    if (SPLIT && wait_fail) atomicCAS(&g_bwd_status, 0, wait_fail);
+    if (SPLIT_A && wait_fail) atomicCAS(&g_bwd_status, 0, wait_fail);
 
     // ---- gradient w.r.t. the segment's start state: decay the first token's totals once more ----------
     if (a.rloc_M) {
@@ -850,7 +844,7 @@ static BwdShape bwd_shape(int KP) {
 // Warps per CTA: 8 when d_v is long enough to use them and the shared-memory layout fits, else 4.
 struct BwdConfig {
     BwdShape s;
-    int W, TV, smem;
+    int W, TV, smem, kbuf;
 };
 static BwdConfig bwd_config(const palimpsa_problem& p) {
     BwdConfig c{};
@@ -871,7 +865,12 @@ static BwdConfig bwd_config(const palimpsa_problem& p) {
     for (;;) {
         c.W = W;
         c.TV = W * rpw;
-        c.smem = bwd_smem_layout(KP, c.TV, c.s.RV * c.s.RK, 32 * W, W * VG, es, unc).total;
+        c.kbuf = 2;
+        c.smem = bwd_smem_layout(KP, c.TV, c.s.RV * c.s.RK, 32 * W, W * VG, es, unc, 2).total;
+        if (c.smem > 227 * 1024) {
+            c.kbuf = 1;
+            c.smem = bwd_smem_layout(KP, c.TV, c.s.RV * c.s.RK, 32 * W, W * VG, es, unc, 1).total;
+        }
         if (c.smem <= 227 * 1024 || W == 4 || rpw == 1 || W >= 11) break;
         W = 4;
     }
@@ -912,7 +911,7 @@ static int launch_bwd_w(const BwdArgs& a, int tiles, int num_seg, bool carry_onl
     constexpr int VG = 32 / KG, TV = W * VG * RV;
     const palimpsa_problem& p = a.p;
     const bool unc = (p.flags & PALIMPSA_FLAG_UNCERTAINTY) != 0;
-    const BwdSmem L = bwd_smem_layout(RK * KG, TV, RV * RK, 32 * W, W * VG, dtype_size(p.io_dtype), unc);
+    const BwdSmem L = bwd_smem_layout(RK * KG, TV, RV * RK, 32 * W, W * VG, dtype_size(p.io_dtype), unc, a.kbuf);
     if (L.total > 227 * 1024) return PALIMPSA_E_DIM;
     dim3 grid(tiles, p.num_seqs * p.H, num_seg);
     dim3 block(32 * W, 1, 1);
@@ -933,8 +932,10 @@ static int launch_bwd_w(const BwdArgs& a, int tiles, int num_seg, bool carry_onl
 }
 
 template <int RK, int KG, int RV>
-static int launch_bwd_t(const BwdArgs& a, int tiles, int num_seg, bool carry_only, cudaStream_t stream) {
-    const BwdConfig cfg = bwd_config(a.p);
+static int launch_bwd_t(const BwdArgs& args, int tiles, int num_seg, bool carry_only, cudaStream_t stream) {
+    const BwdConfig cfg = bwd_config(args.p);
+    BwdArgs a = args;
+    a.kbuf = cfg.kbuf;
     if (cfg.W == 8) return launch_bwd_w<RK, KG, RV, 8>(a, tiles, num_seg, carry_only, stream);
     if constexpr (RK == 4 && KG == 32 && RV == 2) {
         if (cfg.W == 12) return launch_bwd_w<RK, KG, RV, 12>(a, tiles, num_seg, carry_only, stream);
