@@ -250,8 +250,8 @@ def kernel_roofline(d, cfg, steps, peaks):
     achieved = alg_bytes / (ms * 1e-3) / 1e9
     return {"bound": "hbm", "kernel": "bwd_kernel (backward main)", "achieved": achieved, "peak": peaks["hbm_gbs"],
             "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
-            # dram__bytes_read+write of one launch: ncu capture of the half batch (1 557.6 MB, profiles/), doubled
-            "traffic": 2 * 1557.6e6 * (th / 196608.0),
+            # dram__bytes_read+write of one launch: ncu capture of the half batch (1 555.7 MB, profiles/), doubled
+            "traffic": 2 * 1555.7e6 * (th / 196608.0),
             "launch_ms": ms, "algorithmic_bytes_per_launch": alg_bytes,
             "note": "the kernel is FP32-pipe bound, not HBM bound: see 'compute'",
             "compute": {"algorithmic_tflops": flops / (ms * 1e-3) / 1e12, "flop_per_token_head": 30 * K * V}}
