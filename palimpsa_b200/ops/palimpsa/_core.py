@@ -139,8 +139,9 @@ def fwd_op(q: Tensor, k: Tensor, v: Tensor, b: Tensor, gt: Tensor, g: Tensor, Ip
         prm.final_mu, prm.final_I = _ptr(fmu), _ptr(fI)
         prm.ckpt_M, prm.ckpt_I = _ptr(ckM), _ptr(ckI)
         decay = None
-        if num_segments > 1 and cu_seqlens is None and T > 0:
-            # summaries of every segment -> boundary scan -> all segments run side by side
+        if num_segments > 1 and T > 0:
+            # summaries of every segment -> boundary scan -> all segments run side by side; in a packed batch
+            # (T = all tokens) a segment index beyond a sequence's end is an empty segment
             sg, bufs = make_segments(N, num_segments, segment_len(T, num_segments), H, V, K, dev, fwd=True)
             st = _stream(q)
             L.check(lib.palimpsa_segment_summary(C.byref(prm.p), C.byref(sg), st), "palimpsa segment summary")
@@ -171,7 +172,7 @@ def _(q, k, v, b, gt, g, Ip, init_mu, init_I, cu_seqlens, scale, uncertainty, sa
     fI = q.new_empty((N, H, V, K) if want_final else (0,), **f32)
     cs = (_ckpt_slots(B * T, N), H, V, padded_k(K)) if save_ckpt else (0,)
     coff = q.new_empty((N,) if cu_seqlens is not None else (0,), dtype=torch.int32)
-    seg = num_segments > 1 and cu_seqlens is None and T > 0
+    seg = num_segments > 1 and T > 0
     decay = q.new_empty((N, num_segments, H) if seg else (0,), **f32)
     return o, o_var, fmu, fI, q.new_empty(cs, **f32), q.new_empty(cs, **f32), coff, decay
 
@@ -205,7 +206,8 @@ def bwd_op(do: Tensor, do_var: Optional[Tensor], q: Tensor, k: Tensor, v: Tensor
             # state-gradient pass per segment -> reverse boundary scan -> full backward per segment
             G = seg_decay.shape[1]
             V = v.shape[-1]
-            sg, bufs = make_segments(B, G, segment_len(T, G), H, V, K, dev, fwd=False)
+            N = B if cu_seqlens is None else cu_seqlens.numel() - 1
+            sg, bufs = make_segments(N, G, segment_len(T, G), H, V, K, dev, fwd=False)
             sg.decay = seg_decay.data_ptr()
             st = _stream(q)
             if lib.palimpsa_carry_apply_supported(C.byref(prm.p)) and not os.environ.get("PALIMPSA_CARRY_SIMT"):

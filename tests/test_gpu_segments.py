@@ -10,13 +10,15 @@ from tests.helpers import TOL_BF16, TOL_FP32
 pytestmark = pytest.mark.gpu
 
 
-def _run(inp, G, unc=False, mu0=None, I0=None):
+def _run(inp, G, unc=False, mu0=None, I0=None, cu=None):
     from palimpsa_b200.ops import chunk_palimpsa
     names = ("q", "k", "v", "b", "gt", "g", "Ip")
     leaves = {n: inp[n].to(DEV).clone().requires_grad_(True) for n in names}
     kw = dict(output_final_state=True, output_uncertainty=unc, num_segments=G)
     if mu0 is not None:
         kw.update(initial_mu_state=mu0.to(DEV), initial_I_state=I0.to(DEV))
+    if cu is not None:
+        kw["cu_seqlens"] = torch.as_tensor(cu, dtype=torch.int32, device=DEV)
     out, fmu, fI = chunk_palimpsa(*[leaves[n] for n in names], **kw)
     res = {"final_mu": fmu, "final_I": fI}
     if unc:
@@ -48,6 +50,19 @@ def test_segments_with_initial_state_and_slow_decay():
     got = _run(inp, 5, mu0=mu0, I0=I0)
     ref = run_oracle(inp, mu0=mu0, I0=I0)
     compare(got, ref, TOL_FP32, what="segments + init")
+
+
+@pytest.mark.parametrize("dtype,G", [(torch.float32, 4), (torch.float32, 9), (torch.bfloat16, 4)])
+def test_segments_in_a_packed_batch(dtype, G):
+    """Packed sequences of very different lengths (one empty): a segment index past a sequence's end is an
+    empty segment; every sequence still starts from the prior / its own initial state."""
+    cu = [0, 40, 41, 300, 300, 811, 1024]
+    inp = orc.make_inputs(21, B=1, T=1024, H=2, K=64, V=64, dtype=dtype)
+    inp["gt"] = inp["gt"] * 0.1
+    mu0, I0 = orc.make_states(5, len(cu) - 1, 2, 64, 64, inp["Ip"])
+    got = _run(inp, G, unc=(dtype == torch.float32), mu0=mu0, I0=I0, cu=cu)
+    ref = run_oracle(inp, unc=(dtype == torch.float32), mu0=mu0, I0=I0, cu=cu)
+    compare(got, ref, TOL_FP32 if dtype == torch.float32 else TOL_BF16, what=f"packed + segments {dtype} G={G}")
 
 
 def test_segments_bf16_match_unsegmented():
