@@ -16,7 +16,10 @@
 // Reductions: over d_k (dv, db) by xor-shuffles inside the lanes of a row; over d_v (dq, dk) first
 // in registers across a thread's rows, then across the CTA's row groups through shared memory, and
 // across the CTAs of different row tiles through fp32 partial buffers in the workspace, which the
-// finishing kernel sums in a fixed order (bitwise reproducible; no atomics).
+// finishing kernel sums in a fixed order (bitwise reproducible; no atomics).  The CTA-wide barriers of
+// the shared-memory step are mbarriers split into arrive / wait halves (bounded waits), so that the
+// warps of the single resident CTA do not alternate in lockstep between FP32 work and reductions.
+// One CTA per SM: 11 or 12 warps at d_k = 128 (22- or 24-row tiles, whichever pads d_v less).
 //
 // Finishing kernels: (1) per (token, head) row: sum the row tiles, cast dq/dk, form
 // dgt = -g f df and the per-row terms of dg and dIp; (2) per head: ordered sum over rows.

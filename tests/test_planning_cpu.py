@@ -1,0 +1,46 @@
+"""Host-side planning logic that needs no GPU: segment planning, slice widths, shard bounds."""
+import pytest
+
+
+def test_plan_segments():
+    from palimpsa_b200.ops.palimpsa._core import plan_segments, segment_len
+    assert plan_segments(8, 4096, 6, 128, 128) == 1        # 384 (sequence, head, tile) CTAs fill the GPU
+    assert plan_segments(4, 4096, 6, 128, 128) == 1        # 192 CTAs: still above the SM count
+    assert plan_segments(3, 4096, 6, 128, 128) == 16       # 144 CTAs: 256-token segments
+    assert plan_segments(1, 131072, 12, 128, 128) == 32    # long sequence: capped at 32 pieces
+    assert plan_segments(1, 1024, 2, 64, 64) == 1          # short sequences never
+    assert plan_segments(1, 2048, 1, 64, 64) == 8
+    for T, G in ((4096, 16), (333, 3), (17, 4), (1, 1)):
+        L = segment_len(T, G)
+        assert L % 16 == 0 and L * G >= T and L >= 16
+
+
+def test_ramped_widths():
+    from palimpsa_b200.host_pipeline import ramped_widths
+    assert ramped_widths(8) == [1, 2, 2, 2, 1]
+    assert ramped_widths(9, middle=3) == [1, 3, 3, 1, 1]
+    assert ramped_widths(1) == [1] and ramped_widths(2) == [1, 1]
+    for b in range(1, 40):
+        w = ramped_widths(b)
+        assert sum(w) == b and min(w) >= 1 and w[0] == 1 and w[-1] == 1
+
+
+def test_shard_bounds_cover_without_overlap():
+    from palimpsa_b200.parallel import shard_bounds
+    for n in (0, 1, 7, 8, 131072):
+        for world in (1, 2, 3, 8):
+            spans = [shard_bounds(n, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            sizes = [hi - lo for lo, hi in spans]
+            assert max(sizes) - min(sizes) <= 1
+
+
+def test_layer_wrappers_reject_cpu_tensors():
+    import torch
+    from palimpsa_b200.layers import layer_epilogue, layer_prologue
+    x = torch.zeros(1, 2, 2, 8)
+    with pytest.raises(RuntimeError):
+        layer_epilogue(x, None, None, torch.ones(8))
+    with pytest.raises(RuntimeError):
+        layer_prologue(x, x, x, x, torch.zeros(1, 2, 2), torch.zeros(1, 2, 2), torch.zeros(2), torch.zeros(2))
