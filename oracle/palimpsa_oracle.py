@@ -26,8 +26,7 @@ Conventions
 """
 from __future__ import annotations
 
-import math
-from typing import Dict, Optional, Sequence, Tuple
+from typing import Dict, Sequence
 
 import torch
 

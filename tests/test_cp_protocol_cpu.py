@@ -21,7 +21,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _init(rank, world, port, timeout_s=60):
+def _init(rank, world, port, timeout_s=180):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -71,7 +71,10 @@ def _cp_worker(rank, world, port, q_out):
             res["dIp"] = res["dIp"] + res["dI0"].sum((0, 2, 3))
         pg = torch.stack([res["dg"], res["dIp"]])
         dist.all_reduce(pg)
-        q_out.put((rank, lo, hi, o, {n: res[n] for n in ("dq", "dk", "dv", "db", "dgt")}, pg, mu, I))
+        # results travel as numpy arrays (pickled bytes): torch tensors would be passed as shared-memory handles
+        # that die with this process if the parent has not opened them yet
+        q_out.put((rank, lo, hi, o.numpy(), {n: res[n].numpy() for n in ("dq", "dk", "dv", "db", "dgt")}, pg.numpy(),
+                   mu.numpy(), I.numpy()))
         dist.barrier()
         dist.destroy_process_group()
     except Exception:
@@ -87,12 +90,14 @@ def test_cp_chain_matches_single_process(world):
     procs = [ctx.Process(target=_cp_worker, args=(r, world, port, q_out)) for r in range(world)]
     for p in procs:
         p.start()
-    got = [q_out.get(timeout=180) for _ in range(world)]
+    got = [q_out.get(timeout=400) for _ in range(world)]
     for p in procs:
         p.join(60)
     for g in got:
         assert g[1] != "error", g[2]
     got.sort(key=lambda x: x[0])
+    tt = torch.from_numpy
+    got = [(g[0], g[1], g[2], tt(g[3]), {n: tt(x) for n, x in g[4].items()}, tt(g[5]), tt(g[6]), tt(g[7])) for g in got]
     B, T, H, K, V = 2, 45, 2, 4, 6
     d = orc.make_inputs(11, B=B, T=T, H=H, K=K, V=V, dtype=torch.float64)
     d["gt"] = d["gt"] * 0.2
@@ -108,8 +113,9 @@ def test_cp_chain_matches_single_process(world):
 
 def _fail_worker(rank, world, port, q_out):
     try:
-        _init(rank, world, port, timeout_s=4)
+        _init(rank, world, port)       # generous rendezvous: the ranks' start-up times differ under load
         from palimpsa_b200.parallel import chain_down
+        short = dist.new_group(ranks=list(range(world)), timeout=datetime.timedelta(seconds=4))
         like = torch.zeros(2, 1, 1, 2, 2, dtype=torch.float64)
 
         def local(inc):
@@ -118,7 +124,7 @@ def _fail_worker(rank, world, port, q_out):
             return like
 
         try:
-            chain_down(rank, world, None, local, like)
+            chain_down(rank, world, short, local, like)
             q_out.put((rank, "finished"))
         except Exception as e:  # noqa: BLE001
             q_out.put((rank, "raised", type(e).__name__, str(e)[:200]))
@@ -137,7 +143,7 @@ def test_cp_peer_failure_surfaces_as_error_not_hang():
     procs = [ctx.Process(target=_fail_worker, args=(r, 2, port, q_out)) for r in range(2)]
     for p in procs:
         p.start()
-    got = sorted([q_out.get(timeout=120) for _ in range(2)], key=lambda x: x[0])
+    got = sorted([q_out.get(timeout=400) for _ in range(2)], key=lambda x: x[0])
     for p in procs:
         p.join(60)
     assert got[0][1] == "raised" and "fails before" in got[0][3]

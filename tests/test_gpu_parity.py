@@ -6,7 +6,7 @@ import torch
 
 from oracle import palimpsa_oracle as orc
 from tests.gpu_util import DEV, compare, run_cuda, run_oracle, tol_for
-from tests.helpers import GOLDEN_CASES, GOLDEN_TOL, GRADS, TOL_BF16, TOL_FP32, load_golden
+from tests.helpers import GOLDEN_CASES, GOLDEN_TOL, TOL_BF16, TOL_FP32, load_golden
 
 pytestmark = pytest.mark.gpu
 

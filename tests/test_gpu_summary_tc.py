@@ -11,7 +11,6 @@ pytestmark = pytest.mark.gpu
 
 
 def _summaries(inp, G, env_simt):
-    import os
     from palimpsa_b200 import _lib as L
     from palimpsa_b200.ops.palimpsa import _core
     lib = L.lib()
