@@ -243,6 +243,20 @@ def kernel_roofline(d, cfg, steps, peaks):
         torch.cuda.synchronize()
         times.append(e0.elapsed_time(e1))
     ms = sum(times) / len(times)
+    # the other kernels of a step, each timed alone the same way: finishing kernels, forward (checkpoints on)
+    fin, fwd = [], []
+    for _ in range(max(3, steps)):
+        e0, e1, e2 = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e0.record(stream)
+        L.check(lib.palimpsa_chunk_bwd_stages(C.byref(prm), sp, 2), "bwd finish")
+        e1.record(stream)
+        with torch.no_grad():
+            _core.fwd_op(q, k, v, b, gt, g, Ip, None, None, None, K ** -0.5, False, True, False, False, 1)
+        e2.record(stream)
+        torch.cuda.synchronize()
+        fin.append(e0.elapsed_time(e1))
+        fwd.append(e1.elapsed_time(e2))
+    ms_fin, ms_fwd = sum(fin) / len(fin), sum(fwd) / len(fwd)
     th = B * T * H                                   # token-heads per launch
     es = q.element_size()
     alg_bytes = th * ((2 * K + 3 * V) * es + 4 + (2 * K + 2 * V) * es + 4)   # q,k,v,b,do,gt in; dq,dk,dv,db,dgt out
@@ -254,7 +268,10 @@ def kernel_roofline(d, cfg, steps, peaks):
             "traffic": 2 * 1555.7e6 * (th / 196608.0),
             "launch_ms": ms, "algorithmic_bytes_per_launch": alg_bytes,
             "note": "the kernel is FP32-pipe bound, not HBM bound: see 'compute'",
-            "compute": {"algorithmic_tflops": flops / (ms * 1e-3) / 1e12, "flop_per_token_head": 30 * K * V}}
+            "compute": {"algorithmic_tflops": flops / (ms * 1e-3) / 1e12, "flop_per_token_head": 30 * K * V},
+            "other_kernels": {"fwd_kernel": {"launch_ms": ms_fwd, "reciprocals_per_launch": th * K * V,
+                                             "trcp_per_s": th * K * V / (ms_fwd * 1e-3) / 1e12},
+                              "bwd_finish_rows+heads": {"launch_ms": ms_fin}}}
 
 
 def fp32_peaks(dev):
@@ -350,6 +367,8 @@ def run_ours(args, rank, world, local_rank):
         roof["compute"].update({"fp32_fma_peak_tflops_measured": fp["fma_tflops"],
                                 "mufu_rcp_peak_tops_measured": fp["rcp_tops"],
                                 "frac_of_fp32_peak": roof["compute"]["algorithmic_tflops"] / fp["fma_tflops"]})
+        fk = roof["other_kernels"]["fwd_kernel"]
+        fk["frac_of_mufu_peak"] = fk["trcp_per_s"] / fp["rcp_tops"]
     del d
     torch.cuda.empty_cache()
     cpu_line = None                                   # the CPU port is timed beside the one-GPU run only
