@@ -35,7 +35,8 @@ def ramped_widths(batch: int, middle: int = 2):
 class HostPipeline:
     """Reusable pipeline for one problem shape.  ``run(host)`` takes pinned CPU tensors ``q,k,v,b,do``
     ``[B,T,H,*]``, ``gt [B,T,H]``, ``g,Ip [H]`` and returns pinned CPU tensors ``o, dq, dk, dv, db, dgt,
-    dg, dIp``; it returns after everything has landed on the host."""
+    dg, dIp``; it returns after everything has landed on the host.  The returned pinned tensors belong to the
+    pipeline and are overwritten by the next ``run``: copy what must outlive it."""
 
     def __init__(self, host: Dict[str, torch.Tensor], device, slices: Union[int, Sequence[int]] = 4):
         """``slices``: a count (even split of the batch) or the slice widths themselves, e.g. ``(1, 2, 2,
