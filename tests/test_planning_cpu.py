@@ -44,3 +44,12 @@ def test_layer_wrappers_reject_cpu_tensors():
         layer_epilogue(x, None, None, torch.ones(8))
     with pytest.raises(RuntimeError):
         layer_prologue(x, x, x, x, torch.zeros(1, 2, 2), torch.zeros(1, 2, 2), torch.zeros(2), torch.zeros(2))
+
+
+def test_missing_library_is_a_loud_error(monkeypatch, tmp_path):
+    """No CPU or PyTorch fallback: without the built CUDA library every entry fails with a clear message."""
+    from palimpsa_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "libpalimpsa_b200.so"))
+    with pytest.raises(_lib.PalimpsaLibraryError, match="no CPU or PyTorch fallback"):
+        _lib.lib()
