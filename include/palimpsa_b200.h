@@ -37,7 +37,7 @@
 extern "C" {
 #endif
 
-#define PALIMPSA_ABI_VERSION 6
+#define PALIMPSA_ABI_VERSION 7
 
 /* io dtype of q, k, v, b, o, o_var, do, do_var, dq, dk, dv, db */
 #define PALIMPSA_F32 0
@@ -60,6 +60,7 @@ extern "C" {
 #define PALIMPSA_E_ALIGN (-7)       /* a state/workspace pointer is not 16-byte aligned */
 #define PALIMPSA_E_VERSION (-8)     /* struct_size does not match this library */
 #define PALIMPSA_E_LIMIT (-9)       /* problem exceeds a fixed capacity of the entry point */
+#define PALIMPSA_E_SYMBOL (-10)     /* the library's own scratch array could not be located on this device */
 
 #define PALIMPSA_MAX_K 256
 #define PALIMPSA_CKPT_INTERVAL 16   /* tokens between saved (M, I) checkpoints */
@@ -135,10 +136,14 @@ typedef struct palimpsa_segments {
 /* Fills sum_M, sum_J and decay for every segment (no reciprocal, no output: the cheap pass). */
 int palimpsa_segment_summary(const palimpsa_problem *p, const palimpsa_segments *segs, void *cuda_stream);
 
-/* Diagnostic: 0 unless a bounded wait inside a kernel ever gave up on this device; then the code of the
- * wait (1, 2: tensor-core summary kernel; 3, 4: tensor-core carried-gradient kernel; 5, 6: barriers of the
- * backward main kernel).  Every in-kernel wait of this library is bounded: a kernel that gives up records
- * the code, releases what it holds and returns, and its results are then invalid.  Synchronises the device. */
+/* Diagnostic: 0 unless a bounded wait inside a kernel gave up on this device since the last call of this
+ * function; then the code of the wait (1, 2: tensor-core summary kernel; 3, 4: tensor-core carried-gradient
+ * kernel; 5, 6: barriers of the backward main kernel).  Every in-kernel wait of this library is bounded: a
+ * kernel that gives up records the code, releases what it holds and returns.  Its results are invalid, and it
+ * marks them so that the failure cannot pass unnoticed: the summary kernel writes NaN into the segment's decay
+ * (every later output becomes NaN), the other two write NaN into the decay-gradient partials (dgt of the
+ * affected tokens and dg come out NaN).  Synchronises the device; reading clears the recorded code, so a
+ * non-zero value belongs to the work enqueued since the previous call. */
 int palimpsa_tensor_core_status(void);
 
 /* Forward boundary scan: start_M/start_I of every segment from the summaries.  The state before
@@ -187,6 +192,12 @@ const char *palimpsa_last_error_string(int code);
 /* K rounded up to the kernels' tile width (16, 32, 48, 64, 96, 128, 192 or 256); 0 if K > 256. */
 int palimpsa_padded_k(int K);
 
+/* State rows (d_v) that one CTA of the forward kernel owns at head dimensions (K, V); 0 if d_k is not
+ * supported.  A forward launch has ceil(V / rows) x num_seqs x H CTAs (times the segment count): hosts use it
+ * to decide whether a problem fills the GPU or should be cut into segments.  No counterpart in the reference,
+ * whose grid is fixed at (V/16) x N x H programs (chunk_palimpsa_forgetting_scalar.py:478). */
+int palimpsa_fwd_tile_rows(int K, int V);
+
 /* Upper bound on checkpoint slots for a problem: ceil(total_tokens/16) + num_seqs (varlen needs
  * no host synchronisation to size its buffers). */
 long long palimpsa_ckpt_slots(const palimpsa_problem *p);
@@ -223,9 +234,15 @@ int palimpsa_chunk_bwd_stages(const palimpsa_bwd_params *params, void *cuda_stre
  * loads the library for as long as the process lives.  The caller still passes every input and
  * output buffer.  It calls no cudaMalloc, cudaFree or any allocating routine.
  *   - Problems whose palimpsa_bwd_workspace_bytes() exceeds the capacity return PALIMPSA_E_LIMIT
- *     (at d_k = d_v = 128 the capacity covers about 8000 (token, head) rows).
+ *     (at d_k = d_v = 128 the capacity covers about 9900 (token, head) rows: 6720 bytes per row).
  *   - The first call on each device looks up the array's device address (once per device, with that
- *     device current); make that first call outside any stream capture.
+ *     device current); make that first call outside any stream capture.  With the CUDA runtime's
+ *     default lazy module loading the 64 MiB are only reserved when the library's backward code is first
+ *     loaded on a device, which can be this very call: on a device whose memory is already handed out
+ *     the look-up then fails and the call returns PALIMPSA_E_SYMBOL without launching anything.  Hosts
+ *     with a fixed pool should therefore make one small call at start-up, before they carve up the
+ *     device.  The address is cached per device ordinal: only the device's primary context (the one the
+ *     CUDA runtime uses) is supported.
  *   - All calls share the one array, which keeps whatever the previous call left in it.  Nothing in
  *     it has to start at zero: each call's main kernel writes every byte its finishing kernels read.
  *     Two calls that overlap on the GPU (different streams, or threads) race on it; serialise them.

@@ -68,13 +68,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    mb = os.path.join(PKG, "libpalimpsa_microbench.so")
-    r = subprocess.run([_nvcc(), *NVCC_FLAGS, "-shared", os.path.join(CSRC, "microbench.cu"), "-o", mb],
-                       capture_output=True, text=True)
-    if r.returncode != 0:
-        raise RuntimeError(f"nvcc failed on microbench.cu:\n{r.stdout}\n{r.stderr}")
     if verbose:
-        print("built", LIB, "and", mb)
+        print("built", LIB)
     return LIB
 
 

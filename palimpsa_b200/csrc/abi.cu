@@ -1,6 +1,5 @@
 // extern "C" surface of libpalimpsa_b200.so: argument validation and dispatch.  No kernel lives
 // here; see fwd.cu and bwd.cu.
-#include <cstdlib>
 
 #include "common.cuh"
 #include "host.h"
@@ -92,6 +91,7 @@ const char* palimpsa_last_error_string(int code) {
         case PALIMPSA_E_ALIGN: return "a state or checkpoint pointer is not 16-byte aligned";
         case PALIMPSA_E_VERSION: return "struct_size does not match this library (header/library mismatch)";
         case PALIMPSA_E_LIMIT: return "problem exceeds a fixed capacity of this entry point";
+        case PALIMPSA_E_SYMBOL: return "the library's own scratch array could not be located on the current device";
         default: return "unknown error code";
     }
 }
@@ -102,6 +102,11 @@ int palimpsa_padded_k(int K) {
     for (int s : sizes)
         if (K <= s) return s;
     return 0;
+}
+
+int palimpsa_fwd_tile_rows(int K, int V) {
+    if (K <= 0 || V <= 0 || K > PALIMPSA_MAX_K) return 0;
+    return fwd_tile_rows(K, V);
 }
 
 long long palimpsa_ckpt_slots(const palimpsa_problem* p) {
@@ -140,8 +145,7 @@ int palimpsa_segment_summary(const palimpsa_problem* p, const palimpsa_segments*
     rc = check_segments(*p, sg);
     if (rc) return rc;
     if (!sg->sum_M || !sg->sum_J || !sg->decay) return PALIMPSA_E_NULL;
-    static const bool force_simt = getenv("PALIMPSA_SUMMARY_SIMT") != nullptr;  // development switch
-    if (!force_simt && summary_tc_supported(*p)) return launch_summary_tc(*p, *sg, static_cast<cudaStream_t>(cuda_stream));
+    if (summary_tc_supported(*p)) return launch_summary_tc(*p, *sg, static_cast<cudaStream_t>(cuda_stream));
     palimpsa_fwd_params prm{};
     prm.struct_size = sizeof(prm);
     prm.p = *p;
@@ -149,9 +153,9 @@ int palimpsa_segment_summary(const palimpsa_problem* p, const palimpsa_segments*
 }
 
 int palimpsa_tensor_core_status(void) {
-    int s = summary_tc_status();
-    if (!s) s = carry_tc_status();
-    return s ? s : bwd_wait_status();
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    const int a = summary_tc_status(), b = carry_tc_status(), c = bwd_wait_status();  // each clears what it read
+    return a ? a : (b ? b : c);
 }
 
 int palimpsa_carry_apply_supported(const palimpsa_problem* p) { return p && carry_tc_supported(*p) ? 1 : 0; }

@@ -23,7 +23,6 @@
 //
 // Finishing kernels: (1) per (token, head) row: sum the row tiles, cast dq/dk, form
 // dgt = -g f df and the per-row terms of dg and dIp; (2) per head: ordered sum over rows.
-#include <cstdlib>
 #include <mutex>
 
 #include "host.h"
@@ -707,7 +706,13 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
         // the next iteration's first barrier orders these reads before the buffers are reused
     }
 
-    if (SPLIT_A && wait_fail) atomicCAS(&g_bwd_status, 0, wait_fail);
+    if (SPLIT_A && wait_fail) {
+        // a barrier wait ran out: record it and mark this CTA's results as invalid (NaN in the decay-gradient
+        // partial of its first token, which the finishing kernels carry into dgt and dg)
+        atomicCAS(&g_bwd_status, 0, wait_fail);
+        if (tid == 0)
+            a.df_part[(size_t)tile * a.rows_total + (size_t)((long long)bos + s0) * p.H + h] = __int_as_float(0x7fc00000);
+    }
 
     // ---- gradient w.r.t. the segment's start state: decay the first token's totals once more ----------
     if (a.rloc_M) {
@@ -857,13 +862,11 @@ static BwdConfig bwd_config(const palimpsa_problem& p) {
     const bool unc = (p.flags & PALIMPSA_FLAG_UNCERTAINTY) != 0;
     const int es = dtype_size(p.io_dtype);
     int W = (rpw == 1 || p.V > 4 * rpw) ? 8 : 4;
-    static const int force_w = [] { const char* e = getenv("PALIMPSA_BWD_WARPS"); return e ? atoi(e) : 0; }();
-    if (force_w == 4 && rpw > 1) W = 4;
     // d_k = 128: 11 or 12 warps (22 / 24 rows) per CTA hide latency better than 8; of the two, the one that
     // pads d_v with fewer idle rows (d_v = 128: 6 tiles of 22 rows = 132 instead of 144)
-    if (KP == 128 && rpw == 2 && p.V >= 48 && force_w != 8) {
+    if (KP == 128 && rpw == 2 && p.V >= 48) {
         const int pad11 = (p.V + 21) / 22 * 22, pad12 = (p.V + 23) / 24 * 24;
-        W = (pad11 < pad12 && force_w != 12) || force_w == 11 ? 11 : 12;
+        W = pad11 < pad12 ? 11 : 12;
     }
     for (;;) {
         c.W = W;
@@ -952,6 +955,10 @@ int bwd_wait_status() {
     int s = 0;
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
     if (cudaMemcpyFromSymbol(&s, g_bwd_status, sizeof(int)) != cudaSuccess) return -1;
+    if (s) {
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(g_bwd_status, &zero, sizeof(int)) != cudaSuccess) return -1;
+    }
     return s;
 }
 
@@ -1022,8 +1029,8 @@ int launch_bwd(const palimpsa_bwd_params* prm, const palimpsa_segments* segs, bo
 
 // ---- backward with library-owned scratch -----------------------------------------------------------
 // For callers that cannot allocate device memory themselves: the partial-sum scratch of the backward
-// lives in this fixed array instead of a caller-provided workspace.  Every CUDA context that loads the
-// library carries the array until it exits.  Host code may not use the array's name as an address; the
+// lives in this fixed array instead of a caller-provided workspace.  Every device on which the library's
+// backward code gets loaded (primary context) carries the array from then until the process exits.  Host code may not use the array's name as an address; the
 // device address is looked up once per device below.
 static __device__ __align__(256) unsigned char g_static_scratch[PALIMPSA_STATIC_SCRATCH_BYTES];
 
@@ -1041,7 +1048,12 @@ int launch_bwd_static(const palimpsa_bwd_params* prm, cudaStream_t stream) {
         std::lock_guard<std::mutex> lock(mu);
         if (!addr[dev]) {
             void* sym = nullptr;
-            if (cudaGetSymbolAddress(&sym, g_static_scratch) != cudaSuccess || !sym) return PALIMPSA_E_LAUNCH;
+            // may be the call that loads this module on the device (lazy loading): the array is reserved now,
+            // and a device without 64 MiB to spare fails here
+            if (cudaGetSymbolAddress(&sym, g_static_scratch) != cudaSuccess || !sym) {
+                (void)cudaGetLastError();
+                return PALIMPSA_E_SYMBOL;
+            }
             addr[dev] = sym;
         }
         ptr = addr[dev];

@@ -309,7 +309,7 @@ __global__ void __launch_bounds__(128) carry_tc_kernel(const CarryArgs a) {
         const float c_t = lane == 0 ? c_ws : fmaf(Fp, c_ws, Wp);
         if (tid == 127) cnext_s = fmaf(F, c_ws, Wc);
         if (live) {
-            a.df_x[row] = a_t * c_t;
+            a.df_x[row] = status == 0 ? a_t * c_t : __int_as_float(0x7fc00000);  // a wait ran out: mark dgt / dg invalid
             float dip = (1.f - f_t) * a_t * SRI;
             if (t0 + tid == 0 && !has_init) dip += f_t * a_t * SRI;
             a.dip_x[row] = dip;
@@ -364,6 +364,10 @@ int launch_carry_tc(const palimpsa_bwd_params* prm, const palimpsa_segments& sg,
 int carry_tc_status() {
     int s = 0;
     if (cudaMemcpyFromSymbol(&s, g_carry_status, sizeof(int)) != cudaSuccess) return -1;
+    if (s) {
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(g_carry_status, &zero, sizeof(int)) != cudaSuccess) return -1;
+    }
     return s;
 }
 

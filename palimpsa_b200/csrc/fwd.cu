@@ -22,8 +22,6 @@
 // It serves the chunked op and the fused-recurrent op: what the reference does with
 // chunk_palimpsa_fwd_kernel (chunk_palimpsa_forgetting_scalar.py:66-218) and
 // fused_palimpsa_recurrent_fwd_kernel (fused_recurrent_palimpsa.py:24-154).
-#include <cstdlib>
-
 #include "common.cuh"
 #include "host.h"
 
@@ -492,13 +490,45 @@ static int launch_fwd_w(const FwdArgs& a, int num_seg, bool summary, cudaStream_
 
 // Warps per CTA: WMAX, or fewer when d_v is short (the row tile stays a multiple of 8 rows).
 template <int RK, int KG, int RV, int WMAX>
-static int launch_fwd_t(const FwdArgs& a, int num_seg, bool summary, cudaStream_t stream) {
+static int fwd_warps(int V) {
     constexpr int RPW = (32 / KG) * RV;
     if constexpr (WMAX >= 4 && (RPW * (WMAX / 4)) % 8 == 0)
-        if (a.p.V <= RPW * (WMAX / 4)) return launch_fwd_w<RK, KG, RV, WMAX / 4>(a, num_seg, summary, stream);
+        if (V <= RPW * (WMAX / 4)) return WMAX / 4;
     if constexpr (WMAX >= 2 && (RPW * (WMAX / 2)) % 8 == 0)
-        if (a.p.V <= RPW * (WMAX / 2)) return launch_fwd_w<RK, KG, RV, WMAX / 2>(a, num_seg, summary, stream);
+        if (V <= RPW * (WMAX / 2)) return WMAX / 2;
+    return WMAX;
+}
+
+template <int RK, int KG, int RV, int WMAX>
+static int launch_fwd_t(const FwdArgs& a, int num_seg, bool summary, cudaStream_t stream) {
+    const int W = fwd_warps<RK, KG, RV, WMAX>(a.p.V);
+    if constexpr (WMAX >= 4)
+        if (W == WMAX / 4) return launch_fwd_w<RK, KG, RV, WMAX / 4>(a, num_seg, summary, stream);
+    if constexpr (WMAX >= 2)
+        if (W == WMAX / 2) return launch_fwd_w<RK, KG, RV, WMAX / 2>(a, num_seg, summary, stream);
     return launch_fwd_w<RK, KG, RV, WMAX>(a, num_seg, summary, stream);
+}
+
+// The thread tilings, one per padded d_k: X(RK, KG, RV, WMAX).
+#define PALIMPSA_FWD_TILINGS(X)                                                                                \
+    switch (KP) {                                                                                              \
+        case 16: X(8, 2, 2, 2);                                                                                \
+        case 32: X(8, 4, 2, 4);                                                                                \
+        case 48: X(12, 4, 2, 4);                                                                               \
+        case 64: X(16, 4, 2, 2);                                                                               \
+        case 96: X(12, 8, 2, 4);                                                                               \
+        case 128: X(8, 16, 2, 4);                                                                              \
+        case 192: X(12, 16, 2, 4);                                                                             \
+        case 256: X(16, 16, 2, 4);                                                                             \
+        default: break;                                                                                        \
+    }
+
+int fwd_tile_rows(int K, int V) {
+    const int KP = palimpsa_padded_k(K);
+#define PALIMPSA_X(RK, KG, RV, WMAX) return fwd_warps<RK, KG, RV, WMAX>(V) * (32 / KG) * RV
+    PALIMPSA_FWD_TILINGS(PALIMPSA_X)
+#undef PALIMPSA_X
+    return 0;
 }
 
 static bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
@@ -529,27 +559,11 @@ int launch_fwd(const palimpsa_fwd_params* prm, const palimpsa_segments* segs, bo
     const int es = dtype_size(p.io_dtype);
     a.aligned = ((p.K * es) % 16 == 0) && ((p.V * es) % 16 == 0) && aligned16(p.q) && aligned16(p.k) &&
                 aligned16(p.v) && aligned16(p.b) && ((reinterpret_cast<uintptr_t>(p.gt) & 3) == 0);
-    // development knob: PALIMPSA_FWD_CFG=<n> selects an alternative thread tiling for d_k = 128
-    static const int cfg = [] {
-        const char* e = getenv("PALIMPSA_FWD_CFG");
-        return e ? atoi(e) : 0;
-    }();
-    switch (palimpsa_padded_k(p.K)) {
-        case 16: return launch_fwd_t<8, 2, 2, 2>(a, num_seg, summary, stream);
-        case 32: return launch_fwd_t<8, 4, 2, 4>(a, num_seg, summary, stream);
-        case 48: return launch_fwd_t<12, 4, 2, 4>(a, num_seg, summary, stream);
-        case 64: return launch_fwd_t<16, 4, 2, 2>(a, num_seg, summary, stream);
-        case 96: return launch_fwd_t<12, 8, 2, 4>(a, num_seg, summary, stream);
-        case 128:
-            if (cfg == 1) return launch_fwd_t<16, 8, 2, 4>(a, num_seg, summary, stream);
-            if (cfg == 2) return launch_fwd_t<4, 32, 2, 4>(a, num_seg, summary, stream);
-            if (cfg == 3) return launch_fwd_t<4, 32, 4, 4>(a, num_seg, summary, stream);
-            if (cfg == 4) return launch_fwd_t<8, 16, 4, 4>(a, num_seg, summary, stream);
-            return launch_fwd_t<8, 16, 2, 4>(a, num_seg, summary, stream);
-        case 192: return launch_fwd_t<12, 16, 2, 4>(a, num_seg, summary, stream);
-        case 256: return launch_fwd_t<16, 16, 2, 4>(a, num_seg, summary, stream);
-        default: return PALIMPSA_E_DIM;
-    }
+    const int KP = palimpsa_padded_k(p.K);
+#define PALIMPSA_X(RK, KG, RV, WMAX) return launch_fwd_t<RK, KG, RV, WMAX>(a, num_seg, summary, stream)
+    PALIMPSA_FWD_TILINGS(PALIMPSA_X)
+#undef PALIMPSA_X
+    return PALIMPSA_E_DIM;
 }
 
 }  // namespace palimpsa

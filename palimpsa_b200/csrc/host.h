@@ -41,6 +41,9 @@ int launch_combine_bwd(const palimpsa_problem& p, const palimpsa_segments& segs,
 // Backward whose scratch is the library's own fixed device array (bwd.cu).
 int launch_bwd_static(const palimpsa_bwd_params* prm, cudaStream_t stream);
 
+// State rows (d_v) one forward CTA owns at these head dimensions (0: d_k unsupported).
+int fwd_tile_rows(int K, int V);
+
 // State rows (d_v) one backward CTA owns for this problem; the number of row tiles follows.
 int bwd_tile_rows(const palimpsa_problem& p);
 

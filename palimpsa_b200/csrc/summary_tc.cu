@@ -16,8 +16,8 @@
 // No TMA: every operand is transformed in registers on its way (scaled, squared, transposed), so a
 // bulk copy into the MMA layout is not possible; global loads are plain 16-byte coalesced loads.
 // Every wait is bounded; on a timeout the CTA records a status code, frees its TMEM and returns.
-#include "common.cuh"
 #include "host.h"
+#include "tc_common.cuh"
 
 namespace palimpsa {
 
@@ -27,38 +27,8 @@ constexpr int TC_SBO = (TCK / 8) * 128 + 16;   // bytes between 8-row groups of 
 constexpr int TC_LBO = 128;                    // bytes between the K-direction core matrices
 constexpr int TC_OPER = (TC_ROWS / 8) * TC_SBO;  // bytes of one operand tile
 constexpr int TC_STAGE = 4 * TC_OPER;          // A_M, A_J, B_M, B_J
-constexpr unsigned TC_SPIN = 1u << 24;
 
 __device__ int g_tc_status = 0;  // 0 ok; otherwise the first bounded wait that gave up (1: stage, 2: final)
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ unsigned long long umma_desc(unsigned addr) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((addr & 0x3FFFF) >> 4);               // start address
-    d |= (unsigned long long)(TC_LBO >> 4) << 16;                   // leading (K-direction) byte offset
-    d |= (unsigned long long)(TC_SBO >> 4) << 32;                   // stride (row-group) byte offset
-    d |= 1ull << 46;                                                // descriptor version (sm_100)
-    return d;                                                       // layout type 0: no swizzle
-}
-
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-    for (unsigned i = 0; i < TC_SPIN; ++i) {
-        unsigned ok;
-        asm volatile(
-            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
-
-__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
-    __nv_bfloat162 x = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<unsigned*>(&x);
-}
 
 struct TcArgs {
     palimpsa_problem p;
@@ -85,22 +55,16 @@ __global__ void __launch_bounds__(128) summary_tc_kernel(const TcArgs a) {
     const long long seg_base = (((long long)n * G + g) * p.H + h) * V;
 
     if (tid == 0) {
-        for (int i = 0; i < 2; ++i)
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bars[i])));
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        tc::mbar_init(&bars[0]);
+        tc::mbar_init(&bars[1]);
+        tc::mbar_init_fence();
     }
-    if (w == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
-                     "r"(256)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    if (w == 0) tc::tmem_alloc(&tmem_base_s, 256);
+    tc::fence_before_sync();
     __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    tc::fence_after_sync();
     const unsigned tmem = tmem_base_s;
-    // instruction descriptor: D fp32, A/B bf16, both K-major, N = KP, M = 128
-    const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(KP >> 3) << 17) | ((unsigned)(TC_ROWS >> 4) << 24);
+    const unsigned idesc = tc::idesc_bf16(KP);  // D fp32, A/B bf16, both K-major, N = KP, M = 128
 
     const int nblk = (s1 - s0 + TCK - 1) / TCK;
     float logtail = 0.f;  // sum of log f over the tokens after the current block
@@ -128,10 +92,10 @@ __global__ void __launch_bounds__(128) summary_tc_kernel(const TcArgs a) {
         for (int s = 0; s < nt; ++s) blocksum += lf_s[s];
         // ---- the stage must be free: the MMAs that read it two blocks ago have completed ----
         if (use > 0 && status == 0) {
-            if (!mbar_wait(smem_u32(&bars[st]), (use - 1) & 1)) status = 1;
+            if (!tc::mbar_wait(&bars[st], (use - 1) & 1)) status = 1;
         }
         __syncthreads();
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        tc::fence_after_sync();
         // ---- operands: thread (c, tp) handles 8 consecutive rows (chunk c) of a token pair ----
 #pragma unroll 1
         for (int it = 0; it < 4; ++it) {
@@ -153,11 +117,11 @@ __global__ void __launch_bounds__(128) summary_tc_kernel(const TcArgs a) {
                 for (int j = 0; j < 4; ++j) {
                     const float2 fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ua[j]));
                     const float2 fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ub[j]));
-                    *reinterpret_cast<unsigned*>(dst + (2 * j) * 16) = pack_bf16(fa.x * wa, fb.x * wb);
-                    *reinterpret_cast<unsigned*>(dst + (2 * j + 1) * 16) = pack_bf16(fa.y * wa, fb.y * wb);
+                    *reinterpret_cast<unsigned*>(dst + (2 * j) * 16) = tc::pack_bf16(fa.x * wa, fb.x * wb);
+                    *reinterpret_cast<unsigned*>(dst + (2 * j + 1) * 16) = tc::pack_bf16(fa.y * wa, fb.y * wb);
                     if (square) {
-                        *reinterpret_cast<unsigned*>(dst2 + (2 * j) * 16) = pack_bf16(fa.x * fa.x, fb.x * fb.x);
-                        *reinterpret_cast<unsigned*>(dst2 + (2 * j + 1) * 16) = pack_bf16(fa.y * fa.y, fb.y * fb.y);
+                        *reinterpret_cast<unsigned*>(dst2 + (2 * j) * 16) = tc::pack_bf16(fa.x * fa.x, fb.x * fb.x);
+                        *reinterpret_cast<unsigned*>(dst2 + (2 * j + 1) * 16) = tc::pack_bf16(fa.y * fa.y, fb.y * fb.y);
                     }
                 }
             };
@@ -165,33 +129,22 @@ __global__ void __launch_bounds__(128) summary_tc_kernel(const TcArgs a) {
             emit(gb, V, 1, aa, ab, false, 1);   // A_J = a * b
             emit(gk, K, 2, 1.f, 1.f, true, 3);  // B_M = k, B_J = k*k
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        tc::fence_async_smem();
+        tc::fence_before_sync();
         __syncthreads();
         if (tid == 0 && status == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const unsigned sbase = smem_u32(stage);
+            tc::fence_after_sync();
+            const unsigned sbase = tc::smem_u32(stage);
 #pragma unroll
             for (int kk = 0; kk < TCK / 16; ++kk) {
-                const unsigned acc = (i > 0 || kk > 0) ? 1u : 0u;
-                const unsigned long long dAM = umma_desc(sbase + 0 * TC_OPER + kk * 2 * TC_LBO);
-                const unsigned long long dAJ = umma_desc(sbase + 1 * TC_OPER + kk * 2 * TC_LBO);
-                const unsigned long long dBM = umma_desc(sbase + 2 * TC_OPER + kk * 2 * TC_LBO);
-                const unsigned long long dBJ = umma_desc(sbase + 3 * TC_OPER + kk * 2 * TC_LBO);
-                asm volatile(
-                    "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                    "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem),
-                    "l"(dAM), "l"(dBM), "r"(idesc), "r"(acc)
-                    : "memory");
-                asm volatile(
-                    "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                    "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem + 128u),
-                    "l"(dAJ), "l"(dBJ), "r"(idesc), "r"(acc)
-                    : "memory");
+                const bool acc = i > 0 || kk > 0;
+                const unsigned ko = kk * 2 * TC_LBO;
+                tc::mma(tmem, tc::desc(sbase + 0 * TC_OPER + ko, TC_LBO, TC_SBO),
+                        tc::desc(sbase + 2 * TC_OPER + ko, TC_LBO, TC_SBO), idesc, acc);          // S_M += (a v)^T k
+                tc::mma(tmem + 128u, tc::desc(sbase + 1 * TC_OPER + ko, TC_LBO, TC_SBO),
+                        tc::desc(sbase + 3 * TC_OPER + ko, TC_LBO, TC_SBO), idesc, acc);          // S_J += (a b)^T k^2
             }
-            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                             smem_u32(&bars[st]))
-                         : "memory");
+            tc::commit(&bars[st]);
         }
         logtail += blocksum;
     }
@@ -199,10 +152,10 @@ __global__ void __launch_bounds__(128) summary_tc_kernel(const TcArgs a) {
     if (status == 0) {
         for (int st = 0; st < 2; ++st) {
             const int uses = (nblk + 1 - st) / 2;      // blocks that used this stage
-            if (uses > 0 && !mbar_wait(smem_u32(&bars[st]), (uses - 1) & 1)) status = 2;
+            if (uses > 0 && !tc::mbar_wait(&bars[st], (uses - 1) & 1)) status = 2;
         }
     }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    tc::fence_after_sync();
     // ---- accumulators -> global: warp w owns TMEM lanes (= state rows) 32w .. 32w+31 ----
     const int row = 32 * w + lane;
     if (status == 0) {
@@ -211,41 +164,31 @@ __global__ void __launch_bounds__(128) summary_tc_kernel(const TcArgs a) {
             float* dstp = (which ? a.sum_J : a.sum_M);
 #pragma unroll 1
             for (int c0 = 0; c0 < KP; c0 += 32) {
-                unsigned r[32];
+                float r[32];
                 if (nblk > 0) {
-                    const unsigned taddr = tmem + ((unsigned)(32 * w) << 16) + (unsigned)(which * 128 + c0);
-                    asm volatile(
-                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,"
-                        "%26,%27,%28,%29,%30,%31}, [%32];"
-                        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
-                          "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
-                          "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
-                          "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                        : "r"(taddr)
-                        : "memory");
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    tc::tmem_ld32(tmem + ((unsigned)(32 * w) << 16) + (unsigned)(which * 128 + c0), r);
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) r[j] = 0u;   // empty segment: zero summary
+                    for (int j = 0; j < 32; ++j) r[j] = 0.f;   // empty segment: zero summary
                 }
                 if (row < V) {
                     float4* o4 = reinterpret_cast<float4*>(dstp + (seg_base + row) * KP + c0);
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
-                        o4[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                            __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                        o4[j] = make_float4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
                 }
             }
         }
         if (tid == 0) a.decay[((long long)n * G + g) * p.H + h] = __expf(logtail);
     } else if (tid == 0) {
+        // a wait ran out: record it and make the failure visible in the data (a NaN decay poisons every state
+        // and output that depends on this segment)
         atomicCAS(&g_tc_status, 0, status);
+        a.decay[((long long)n * G + g) * p.H + h] = __int_as_float(0x7fc00000);
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    tc::fence_before_sync();
     __syncthreads();
-    if (w == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+    if (w == 0) tc::tmem_free(tmem, 256);
 }
 
 bool summary_tc_supported(const palimpsa_problem& p) {
@@ -274,6 +217,10 @@ int launch_summary_tc(const palimpsa_problem& p, const palimpsa_segments& sg, cu
 int summary_tc_status() {
     int s = 0;
     if (cudaMemcpyFromSymbol(&s, g_tc_status, sizeof(int)) != cudaSuccess) return -1;
+    if (s) {
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int)) != cudaSuccess) return -1;
+    }
     return s;
 }
 

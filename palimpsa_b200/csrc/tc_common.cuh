@@ -46,10 +46,10 @@ __device__ __forceinline__ void mbar_init(unsigned long long* bar) {
 }
 __device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 
-// Wait until the phase with this parity has completed; false if it did not within SPIN_LIMIT polls.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+// Wait until the phase with this parity has completed; false if it did not within `limit` polls.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, unsigned limit = SPIN_LIMIT) {
     const unsigned addr = smem_u32(bar);
-    for (unsigned i = 0; i < SPIN_LIMIT; ++i) {
+    for (unsigned i = 0; i < limit; ++i) {
         unsigned ok;
         asm volatile(
             "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"

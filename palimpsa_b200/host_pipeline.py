@@ -13,6 +13,7 @@ from typing import Dict, Optional, Sequence, Union
 
 import torch
 
+from . import _lib as L
 from .ops import chunk_palimpsa
 
 _IN_BATCHED = ("q", "k", "v", "b", "gt", "do")
@@ -119,6 +120,10 @@ class HostPipeline:
         cur.synchronize()
         s_out.synchronize()
         pending.clear()
+        code = L.lib().palimpsa_tensor_core_status()     # everything has finished: did a bounded in-kernel wait give up?
+        if code:
+            raise RuntimeError(f"palimpsa_b200: a bounded wait inside a kernel gave up (code {code}); "
+                               "the results of this run are invalid")
         return self.out
 
 

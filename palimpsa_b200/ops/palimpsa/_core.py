@@ -7,7 +7,6 @@ stream.  There is no fallback: CPU tensors are rejected and a missing library ra
 from __future__ import annotations
 
 import ctypes as C
-import os
 from typing import Optional, Tuple
 
 import torch
@@ -16,6 +15,11 @@ from torch import Tensor
 from ... import _lib as L
 
 _DT = {torch.float32: L.F32, torch.bfloat16: L.BF16, torch.float16: L.F16}
+
+# Segmented backward: take the tensor-core route for the carried-gradient terms wherever the library supports
+# the problem (bf16, d_v <= 128, padded d_k in {32,64,96,128}).  Tests set this to False to exercise the
+# two-pass CUDA-core route on the same problems.
+carry_on_tensor_cores = True
 
 
 def _ptr(t: Optional[Tensor]):
@@ -70,12 +74,32 @@ def _chunk_offsets(cu_seqlens: Tensor) -> Tensor:
     return (torch.cumsum(nblk, 0) - nblk).to(torch.int32)
 
 
-def plan_segments(N: int, T: int, H: int, K: int, V: int) -> int:
+B200_SM_COUNT = 148     # used only when no CUDA device is visible (planning on a build machine)
+_sm_count_cache = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of ``device`` (default: the current CUDA device)."""
+    if not torch.cuda.is_available():
+        return B200_SM_COUNT
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    if idx not in _sm_count_cache:
+        _sm_count_cache[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _sm_count_cache[idx]
+
+
+def plan_segments(N: int, T: int, H: int, K: int, V: int, device=None) -> int:
     """How many segments to cut every sequence into on one GPU.  Segments cost an extra summary pass
     (and the carried-gradient terms in backward), so they are only used when the (sequence, head,
-    row-tile) grid alone would leave SMs idle, e.g. one very long sequence or a narrow batch slice."""
-    ctas = N * H * ((V + 15) // 16)
-    if ctas >= 148 or T < 2048:
+    row-tile) grid of the forward kernel alone would leave SMs idle, e.g. one very long sequence or a narrow
+    batch slice.  The row-tile height comes from the library, the SM count from the device."""
+    rows = L.lib().palimpsa_fwd_tile_rows(int(K), int(V))
+    if rows <= 0:
+        raise ValueError(f"d_k = {K} is above the supported maximum of 256")
+    ctas = N * H * ((V + rows - 1) // rows)
+    if ctas >= sm_count(device) or T < 2048:
         return 1
     # The boundary passes' total work does not depend on the number of segments, and their own grids
     # (one CTA per sequence x head x segment) want many of them: cut down to 256 tokens, at most 32 pieces
@@ -210,7 +234,7 @@ def bwd_op(do: Tensor, do_var: Optional[Tensor], q: Tensor, k: Tensor, v: Tensor
             sg, bufs = make_segments(N, G, segment_len(T, G), H, V, K, dev, fwd=False)
             sg.decay = seg_decay.data_ptr()
             st = _stream(q)
-            if lib.palimpsa_carry_apply_supported(C.byref(prm.p)) and not os.environ.get("PALIMPSA_CARRY_SIMT"):
+            if carry_on_tensor_cores and lib.palimpsa_carry_apply_supported(C.byref(prm.p)):
                 # zero-carry backward of every segment -> reverse boundary scan -> carried terms on the tensor
                 # cores -> finishing kernels
                 L.check(lib.palimpsa_chunk_bwd_segments(C.byref(prm), C.byref(sg), 2, st), "palimpsa backward (main)")
@@ -278,7 +302,7 @@ fwd_op.register_autograd(_backward, setup_context=_setup_context)
 
 
 def run(q, k, v, b, gt, g, Ip, initial_mu_state, initial_I_state, scale, output_final_state, output_uncertainty,
-        cu_seqlens, recurrent: bool, out_dtype, num_segments: Optional[int] = None):
+        cu_seqlens, recurrent: bool, out_dtype, num_segments: Optional[int] = None, var_dtype=None):
     """Shared body of chunk_palimpsa / fused_recurrent_palimpsa: checks, dtype policy, op call, packing."""
     if q.dim() != 4 or k.shape != q.shape or v.dim() != 4 or b.shape != v.shape or v.shape[:3] != q.shape[:3]:
         raise ValueError("expected q,k [B,T,H,K] and v,b [B,T,H,V]")
@@ -301,17 +325,26 @@ def run(q, k, v, b, gt, g, Ip, initial_mu_state, initial_I_state, scale, output_
             raise ValueError(f"initial states must have shape {(N, H, V, K)}")
         initial_mu_state = initial_mu_state.detach().float().contiguous()
         initial_I_state = initial_I_state.detach().float().contiguous()
+    # One io dtype per call: the widest of the four token tensors (the reference's kernels read each tensor in its
+    # own dtype and compute in fp32, so a narrower choice would round an input the reference does not round;
+    # under autocast its layers do pass fp32 q/k next to bf16 v).
     io = q.dtype
+    for x in (k, v, b):
+        io = torch.promote_types(io, x.dtype)
+    if io not in _DT:
+        raise TypeError(f"unsupported dtype combination {[x.dtype for x in (q, k, v, b)]}")
     q, k, v, b = [x.to(io).contiguous() for x in (q, k, v, b)]
     gt, g, Ip = [x.float().contiguous() for x in (gt, g, Ip)]
     save_ckpt = torch.is_grad_enabled() and any(x.requires_grad for x in (q, k, v, b, gt, g, Ip))
     if num_segments is None:
-        num_segments = 1 if cu_seqlens is not None else plan_segments(N, T, H, K, V)
+        num_segments = 1 if cu_seqlens is not None else plan_segments(N, T, H, K, V, q.device)
     o, o_var, fmu, fI, _, _, _, _ = fwd_op(q, k, v, b, gt, g, Ip, initial_mu_state, initial_I_state, cu_seqlens,
                                            float(scale), bool(output_uncertainty), save_ckpt, bool(output_final_state),
                                            recurrent, int(num_segments))
     if out_dtype is not None and out_dtype != o.dtype:
         o = o.to(out_dtype)
+    if output_uncertainty and var_dtype is not None and var_dtype != o_var.dtype:
+        o_var = o_var.to(var_dtype)
     out = (o, o_var) if output_uncertainty else o
     if output_final_state:
         return out, fmu, fI

@@ -30,4 +30,5 @@ def chunk_palimpsa(q, k, v, b, gt, g, Ip, initial_mu_state=None, initial_I_state
     if cu_seqlens is not None and q.shape[0] != 1:
         raise ValueError(f"Batch size must be 1 for Varlen, got {q.shape[0]}")
     return _core.run(q, k, v, b, gt, g, Ip, initial_mu_state, initial_I_state, scale, output_final_state,
-                     output_uncertainty, cu_seqlens, recurrent=False, out_dtype=q.dtype, num_segments=num_segments)
+                     output_uncertainty, cu_seqlens, recurrent=False, out_dtype=q.dtype, num_segments=num_segments,
+                     var_dtype=q.dtype)

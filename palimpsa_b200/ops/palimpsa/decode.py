@@ -8,12 +8,41 @@ the cache tensors themselves.
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
+from torch import Tensor
 
 from ... import _lib as L
 from . import _core
+
+
+@torch.library.custom_op("palimpsa_b200::decode_step", mutates_args=("mu_state", "I_state"), device_types="cuda")
+def decode_step_op(q: Tensor, k: Tensor, v: Tensor, b: Tensor, gt: Tensor, g: Tensor, Ip: Tensor, mu_state: Tensor,
+                   I_state: Tensor, scale: float, uncertainty: bool) -> Tuple[Tensor, Tensor]:
+    """The registered op: contiguous ``[N,1,H,*]`` inputs of one io dtype, float32 ``gt, g, Ip`` and state cache;
+    returns ``(o, o_var)`` (``o_var`` empty without ``uncertainty``) and updates the two cache tensors in place."""
+    N, _, H, K = q.shape
+    V = v.shape[-1]
+    lib = L.lib()
+    with torch.cuda.device(q.device):
+        o = torch.empty(N, 1, H, V, dtype=q.dtype, device=q.device)
+        o_var = torch.empty(N, 1, H, V, dtype=q.dtype, device=q.device) if uncertainty else q.new_empty(0)
+        prm = L.FwdParams()
+        prm.struct_size = C.sizeof(L.FwdParams)
+        prm.p = _core._problem(q, k, v, b, gt, g, Ip, None, None, mu_state, I_state, scale,
+                               L.FLAG_UNCERTAINTY if uncertainty else 0)
+        prm.o, prm.o_var = _core._ptr(o), _core._ptr(o_var)
+        prm.final_mu, prm.final_I = mu_state.data_ptr(), I_state.data_ptr()
+        L.check(lib.palimpsa_decode_step(C.byref(prm), _core._stream(q)), "palimpsa decode step")
+    return o, o_var
+
+
+@decode_step_op.register_fake
+def _(q, k, v, b, gt, g, Ip, mu_state, I_state, scale, uncertainty):
+    N, _, H, _ = q.shape
+    V = v.shape[-1]
+    return q.new_empty(N, 1, H, V), (q.new_empty(N, 1, H, V) if uncertainty else q.new_empty(0))
 
 
 def decode_step(q, k, v, b, gt, g, Ip, mu_state: torch.Tensor, I_state: torch.Tensor, scale: Optional[float] = None,
@@ -21,7 +50,9 @@ def decode_step(q, k, v, b, gt, g, Ip, mu_state: torch.Tensor, I_state: torch.Te
     """One token for each of N sequences: ``q,k [N,1,H,K]`` (or ``[N,H,K]``), ``v,b [N,1,H,V]``,
     ``gt [N,1,H]``, ``g,Ip [H]``; ``mu_state, I_state [N,H,V,K]`` float32 contiguous CUDA tensors that
     are UPDATED IN PLACE.  Returns ``o [N,1,H,V]`` (and ``o_var`` with ``output_uncertainty``).
-    Not differentiable (inference only)."""
+    Not differentiable (inference only).  The work is done by the registered op
+    ``torch.ops.palimpsa_b200.decode_step`` (declared as mutating the two cache tensors), so the call can sit
+    inside a ``torch.compile``d decode loop."""
     if q.dim() == 3:
         q, k, v, b, gt = q.unsqueeze(1), k.unsqueeze(1), v.unsqueeze(1), b.unsqueeze(1), gt.unsqueeze(1)
     N, T, H, K = q.shape
@@ -37,17 +68,7 @@ def decode_step(q, k, v, b, gt, g, Ip, mu_state: torch.Tensor, I_state: torch.Te
     io = q.dtype
     q, k, v, b = [x.detach().to(io).contiguous() for x in (q, k, v, b)]
     gt, g, Ip = [x.detach().float().contiguous() for x in (gt, g, Ip)]
-    lib = L.lib()
-    with torch.cuda.device(q.device):
-        o = torch.empty(N, 1, H, V, dtype=io, device=q.device)
-        o_var = torch.empty(N, 1, H, V, dtype=io, device=q.device) if output_uncertainty else None
-        prm = L.FwdParams()
-        prm.struct_size = C.sizeof(L.FwdParams)
-        prm.p = _core._problem(q, k, v, b, gt, g, Ip, None, None, mu_state, I_state, scale,
-                               L.FLAG_UNCERTAINTY if output_uncertainty else 0)
-        prm.o, prm.o_var = _core._ptr(o), _core._ptr(o_var)
-        prm.final_mu, prm.final_I = mu_state.data_ptr(), I_state.data_ptr()
-        L.check(lib.palimpsa_decode_step(C.byref(prm), _core._stream(q)), "palimpsa decode step")
+    o, o_var = decode_step_op(q, k, v, b, gt, g, Ip, mu_state, I_state, float(scale), bool(output_uncertainty))
     return (o, o_var) if output_uncertainty else o
 
 

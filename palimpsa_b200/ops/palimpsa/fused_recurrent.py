@@ -14,8 +14,9 @@ def fused_recurrent_palimpsa(q, k, v, b, gt, g, Ip, scale: Optional[float] = Non
                              initial_I_state: Optional[torch.Tensor] = None, output_final_state: bool = False,
                              output_uncertainty: bool = False, cu_seqlens: Optional[torch.Tensor] = None):
     """Token-by-token form of the operator, used by the layers for decode and short evaluation
-    sequences (palimpsa/layers/palimpsa.py:221,317).  Output dtype is ``v``'s, as in the reference
-    (:247).  Unlike the reference (:250-253) it is differentiable."""
+    sequences (palimpsa/layers/palimpsa.py:221,317).  ``o`` comes back in ``v``'s dtype and ``o_var`` in
+    float32, as in the reference (:247-248); with 16-bit inputs the kernel writes ``o_var`` in that dtype first,
+    so its float32 values carry that rounding.  Unlike the reference (:250-253) it is differentiable."""
     if cu_seqlens is not None:
         if q.shape[0] != 1:
             raise ValueError(
@@ -25,4 +26,4 @@ def fused_recurrent_palimpsa(q, k, v, b, gt, g, Ip, scale: Optional[float] = Non
     if scale is None:
         scale = k.shape[-1] ** -0.5
     return _core.run(q, k, v, b, gt, g, Ip, initial_mu_state, initial_I_state, scale, output_final_state,
-                     output_uncertainty, cu_seqlens, recurrent=True, out_dtype=v.dtype)
+                     output_uncertainty, cu_seqlens, recurrent=True, out_dtype=v.dtype, var_dtype=torch.float32)

@@ -189,9 +189,7 @@ class _CudaLocal:
         return outs, ws, self._bwd_params(do, ckM, ckI, outs, ws)
 
     def tensor_core_carry(self) -> bool:
-        import os
-        return bool(self.lib.palimpsa_carry_apply_supported(C.byref(self.prob))) and \
-            not os.environ.get("PALIMPSA_CARRY_SIMT")
+        return self.core.carry_on_tensor_cores and bool(self.lib.palimpsa_carry_apply_supported(C.byref(self.prob)))
 
     def backward(self, do, ckM, ckI, sg):
         """Full backward of every local segment with the end-state gradients in sg.carry_*."""
@@ -227,17 +225,23 @@ class _CpChunkPalimpsa(torch.autograd.Function):
         ctx.loc, ctx.group, ctx.reduce = loc, group, reduce_param_grads
         ctx.rank, ctx.world = rank, world
         if need_grad:
-            ctx.save_for_backward(ckM, ckI, loc.bufs["decay"])
-        ctx.mark_non_differentiable(fmu, fI)
+            # the inputs go through save_for_backward as well, so that an in-place change between forward and
+            # backward is detected (the C structs of `loc` hold their raw addresses)
+            ctx.save_for_backward(q, k, v, b, gt, g, Ip, ckM, ckI, loc.bufs["decay"])
+        # ONE call with every non-differentiable output (a second call would replace the first): the final
+        # states never carry a graph, like the reference's (chunk_palimpsa_forgetting_scalar.py:522)
         if o_var is None:
             o_var = o.new_empty(0)
-            ctx.mark_non_differentiable(o_var)
+            ctx.mark_non_differentiable(fmu, fI, o_var)
+        else:
+            ctx.mark_non_differentiable(fmu, fI)
         return o, o_var, fmu, fI
 
     @staticmethod
     def backward(ctx, do, do_var, _dmu, _dI):
         loc = ctx.loc
-        ckM, ckI, decay = ctx.saved_tensors
+        *inputs, ckM, ckI, decay = ctx.saved_tensors       # raises if an input was modified in place meanwhile
+        assert all(x.data_ptr() == y.data_ptr() for x, y in zip(inputs, loc.t))
         io = loc.t[0].dtype
         do = torch.zeros_like(loc.t[2]) if do is None else do.to(io).contiguous()
         if loc.unc:
@@ -280,7 +284,7 @@ def cp_chunk_palimpsa(q, k, v, b, gt, g, Ip, group=None, scale=None, output_fina
     gt, g, Ip = [x.float().contiguous() for x in (gt, g, Ip)]
     B, T, H, K = q.shape
     if num_segments is None:
-        num_segments = _core.plan_segments(B, T, H, K, v.shape[-1])
+        num_segments = _core.plan_segments(B, T, H, K, v.shape[-1], q.device)
     if (initial_mu_state is None) != (initial_I_state is None):
         raise ValueError("pass both initial_mu_state and initial_I_state, or neither")
     if initial_mu_state is not None:

@@ -46,3 +46,35 @@ def test_torch_compile_traces_through_the_op():
     ref = f(*args)
     out = torch.compile(f, backend="aot_eager", fullgraph=True)(*args)
     assert torch.allclose(ref, out)
+
+
+def _decode_args(dtype=torch.bfloat16):
+    N, H, K, V = 3, 2, 32, 16
+    inp = orc.make_inputs(3, B=N, T=1, H=H, K=K, V=V, dtype=dtype)
+    mu, I = orc.make_states(4, N, H, V, K, inp["Ip"])
+    return [inp[n].to(DEV) for n in ("q", "k", "v", "b", "gt", "g", "Ip")] + [mu.to(DEV), I.to(DEV)]
+
+
+def test_opcheck_decode_step_op():
+    """``palimpsa_b200::decode_step`` declares that it mutates the two cache tensors; schema and fake kernel agree."""
+    from palimpsa_b200.ops.palimpsa import decode as D
+    args = (*_decode_args(), 0.25, True)
+    torch.library.opcheck(D.decode_step_op, args, test_utils=("test_schema", "test_faketensor"))
+
+
+def test_torch_compile_decode_loop_updates_the_cache_in_place():
+    from palimpsa_b200.ops import decode_step
+    args = _decode_args()
+    ref_args = [x.clone() for x in args]
+
+    def loop(q, k, v, b, gt, g, Ip, mu, I):
+        o = None
+        for _ in range(3):
+            o = decode_step(q, k, v, b, gt, g, Ip, mu, I)
+        return o + 0.0
+
+    ref = loop(*ref_args)
+    out = torch.compile(loop, backend="aot_eager", fullgraph=True)(*args)
+    assert torch.equal(ref, out)
+    assert torch.equal(args[7], ref_args[7]) and torch.equal(args[8], ref_args[8])      # caches advanced identically
+    assert not torch.equal(args[7], _decode_args()[7])

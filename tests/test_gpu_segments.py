@@ -91,7 +91,8 @@ def test_tensor_core_carry_terms_match_oracle_and_cuda_core_path(monkeypatch):
     ref = run_oracle(inp)
     tc_path = _run(inp, 5)
     assert L.lib().palimpsa_tensor_core_status() == 0
-    monkeypatch.setenv("PALIMPSA_CARRY_SIMT", "1")
+    from palimpsa_b200.ops.palimpsa import _core
+    monkeypatch.setattr(_core, "carry_on_tensor_cores", False)
     simt = _run(inp, 5)
     compare(tc_path, ref, TOL_BF16, what="tensor-core carry vs oracle")
     compare(simt, ref, TOL_BF16, what="CUDA-core carry vs oracle")
