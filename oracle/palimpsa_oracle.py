@@ -135,7 +135,7 @@ def oracle_fwd_bwd(q, k, v, b, gt, g, Ip, do, do_var=None, initial_mu_state=None
 
 
 def oracle_backward_explicit(q, k, v, b, gt, g, Ip, do, do_var=None, initial_mu_state=None,
-                             initial_I_state=None, scale=None, carry_M=None, carry_I=None):
+                             initial_I_state=None, scale=None, carry_M=None, carry_I=None, block=None):
     """Hand-derived backward of one batch of equal-length sequences, float64, no autograd.
 
     This is the recurrence the CUDA backward kernels implement; the reference's version of the same
@@ -147,8 +147,11 @@ def oracle_backward_explicit(q, k, v, b, gt, g, Ip, do, do_var=None, initial_mu_
     is supplied (the kernel's ``:418`` omits that term).
 
     ``carry_M/carry_I`` are optional gradients w.r.t. the END state in (M, I) form (used by the
-    segment / context-parallel identities).  Returns a dict with the 7 gradients plus
-    ``dM0, dI0`` (gradients w.r.t. the start state in (M, I) form).
+    segment / context-parallel identities).  ``block``: keep the per-token states of only that many
+    tokens at a time (states at block starts are kept, each block is walked forward again when the
+    reverse walk reaches it), which bounds the memory for long sequences; the result is the same.
+    Returns a dict with the 7 gradients plus ``dM0, dI0`` (gradients w.r.t. the start state in (M, I)
+    form), ``df`` and the forward's ``o`` and final ``(mu, I)``.
     """
     q, k, v, b, gt, g, Ip, do = [_f64(x) for x in (q, k, v, b, gt, g, Ip, do)]
     do_var = _f64(do_var)
@@ -156,6 +159,8 @@ def oracle_backward_explicit(q, k, v, b, gt, g, Ip, do, do_var=None, initial_mu_
     V = v.shape[-1]
     if scale is None:
         scale = K ** -0.5
+    if block is None or block <= 0:
+        block = max(T, 1)
     ipb = Ip.view(1, H, 1, 1)
     if initial_mu_state is None:
         I = ipb.expand(B, H, V, K).clone()
@@ -164,13 +169,21 @@ def oracle_backward_explicit(q, k, v, b, gt, g, Ip, do, do_var=None, initial_mu_
         I = _f64(initial_I_state).clone()
         M = _f64(initial_mu_state) * I
     f_all = torch.exp(-gt * g.view(1, 1, H))                      # [B,T,H]
-    Ms, Is = [M], [I]
-    for t in range(T):
+
+    def step(M, I, t):
         f = f_all[:, t].view(B, H, 1, 1)
         M = f * M + v[:, t, :, :, None] * k[:, t, :, None, :]
         I = f * I + (1.0 - f) * ipb + b[:, t, :, :, None] * (k[:, t, :, None, :] ** 2)
-        Ms.append(M)
-        Is.append(I)
+        return M, I
+
+    o = torch.zeros_like(v)
+    starts = []                                                    # state before the first token of every block
+    for t in range(T):
+        if t % block == 0:
+            starts.append((M, I))
+        M, I = step(M, I, t)
+        o[:, t] = ((M / I) * (q[:, t] * scale)[:, :, None, :]).sum(-1)
+    final_mu, final_I = M / I, I
     dq = torch.zeros_like(q)
     dk = torch.zeros_like(k)
     dv = torch.zeros_like(v)
@@ -179,41 +192,49 @@ def oracle_backward_explicit(q, k, v, b, gt, g, Ip, do, do_var=None, initial_mu_
     s2 = torch.zeros_like(gt)                                     # sum_{v,k} GI_t
     GM = torch.zeros(B, H, V, K, dtype=F64) if carry_M is None else _f64(carry_M).clone()
     GI = torch.zeros(B, H, V, K, dtype=F64) if carry_I is None else _f64(carry_I).clone()
-    for t in range(T - 1, -1, -1):
-        Mt, It, Mp, Ipv = Ms[t + 1], Is[t + 1], Ms[t], Is[t]
-        r = 1.0 / It
-        mu = Mt * r
-        qs = (q[:, t] * scale)[:, :, None, :]                     # [B,H,1,K]
-        dy = do[:, t][:, :, :, None]                              # [B,H,V,1]
-        dMl = dy * qs * r
-        dIl = -dMl * mu
-        dq[:, t] = scale * (dy * mu).sum(2)
-        if do_var is not None:
-            dyv = do_var[:, t][:, :, :, None]
-            qq = (scale * q[:, t] ** 2)[:, :, None, :]
-            dIl = dIl - dyv * qq * r * r
-            dq[:, t] += 2.0 * scale * q[:, t] * (dyv * r).sum(2)
-        # GM/GI hold f_{t+1} * (total gradient at t+1) when entering the iteration
-        GM = dMl + GM
-        GI = dIl + GI
-        kt = k[:, t][:, :, None, :]
-        vt = v[:, t][:, :, :, None]
-        bt = b[:, t][:, :, :, None]
-        dk[:, t] = (GM * vt).sum(2) + 2.0 * k[:, t] * (GI * bt).sum(2)
-        dv[:, t] = (GM * kt).sum(3)
-        db[:, t] = (GI * kt * kt).sum(3)
-        df[:, t] = (GM * Mp).sum((2, 3)) + (GI * (Ipv - ipb)).sum((2, 3))
-        s2[:, t] = GI.sum((2, 3))
-        f = f_all[:, t].view(B, H, 1, 1)
-        GM = f * GM
-        GI = f * GI
+    for blk in range(len(starts) - 1, -1, -1):
+        t_lo, t_hi = blk * block, min(T, (blk + 1) * block)
+        Ms, Is = [starts[blk][0]], [starts[blk][1]]               # Ms[j] = state before token t_lo + j
+        for t in range(t_lo, t_hi):
+            Mn, In = step(Ms[-1], Is[-1], t)
+            Ms.append(Mn)
+            Is.append(In)
+        for t in range(t_hi - 1, t_lo - 1, -1):
+            Mt, It, Mp, Ipv = Ms[t - t_lo + 1], Is[t - t_lo + 1], Ms[t - t_lo], Is[t - t_lo]
+            r = 1.0 / It
+            mu = Mt * r
+            qs = (q[:, t] * scale)[:, :, None, :]                     # [B,H,1,K]
+            dy = do[:, t][:, :, :, None]                              # [B,H,V,1]
+            dMl = dy * qs * r
+            dIl = -dMl * mu
+            dq[:, t] = scale * (dy * mu).sum(2)
+            if do_var is not None:
+                dyv = do_var[:, t][:, :, :, None]
+                qq = (scale * q[:, t] ** 2)[:, :, None, :]
+                dIl = dIl - dyv * qq * r * r
+                dq[:, t] += 2.0 * scale * q[:, t] * (dyv * r).sum(2)
+            # GM/GI hold f_{t+1} * (total gradient at t+1) when entering the iteration
+            GM = dMl + GM
+            GI = dIl + GI
+            kt = k[:, t][:, :, None, :]
+            vt = v[:, t][:, :, :, None]
+            bt = b[:, t][:, :, :, None]
+            dk[:, t] = (GM * vt).sum(2) + 2.0 * k[:, t] * (GI * bt).sum(2)
+            dv[:, t] = (GM * kt).sum(3)
+            db[:, t] = (GI * kt * kt).sum(3)
+            df[:, t] = (GM * Mp).sum((2, 3)) + (GI * (Ipv - ipb)).sum((2, 3))
+            s2[:, t] = GI.sum((2, 3))
+            f = f_all[:, t].view(B, H, 1, 1)
+            GM = f * GM
+            GI = f * GI
+        del Ms, Is
     dgt = -g.view(1, 1, H) * f_all * df
     dg = (-gt * f_all * df).sum((0, 1))
     dIp = ((1.0 - f_all) * s2).sum((0, 1))
     if initial_mu_state is None:
         dIp = dIp + GI.sum((0, 2, 3))        # I_0 = Ip: the start-state gradient flows into Ip
     return {"dq": dq, "dk": dk, "dv": dv, "db": db, "dgt": dgt, "dg": dg, "dIp": dIp,
-            "dM0": GM, "dI0": GI, "df": df}
+            "dM0": GM, "dI0": GI, "df": df, "o": o, "final_mu": final_mu, "final_I": final_I}
 
 
 # --------------------------------------------------------------------------------------------

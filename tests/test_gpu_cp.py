@@ -1,6 +1,7 @@
 """Context parallelism on real GPUs (needs >= 2): every rank holds a contiguous share of one sequence;
-outputs and gradients must equal the single-GPU op on the whole sequence.  Ranks are child processes,
-one per GPU, NCCL point-to-point for the boundary states (NVLS off: a plain send/recv needs none)."""
+its outputs and gradients must equal the float64 oracle's for the whole sequence, at the operator's stated
+tolerance (1e-5 fp32, 2e-2 bf16).  Ranks are child processes, one per GPU, NCCL point-to-point for the
+boundary states (NVLS off: a plain send/recv needs none)."""
 import os
 import socket
 import sys
@@ -29,25 +30,18 @@ def _worker(rank, world, port, q_out, dtype_name, T, G, extras=False):
         dist.init_process_group("nccl", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120),
                                 device_id=torch.device("cuda", rank))
         from oracle import palimpsa_oracle as orc
-        from palimpsa_b200.ops import chunk_palimpsa
         from palimpsa_b200.parallel import cp_chunk_palimpsa, shard_bounds
         dtype = getattr(torch, dtype_name)
         dev = torch.device("cuda", rank)
         inp = orc.make_inputs(5, B=2, T=T, H=3, K=64, V=48, dtype=dtype)
         inp["gt"] = inp["gt"] * 0.05
         names = ("q", "k", "v", "b", "gt", "g", "Ip")
-        full = {n: inp[n].to(dev).requires_grad_(True) for n in names}
         kw = {}
         if extras:      # explicit initial state (used on the first rank only) and the uncertainty output
             mu0, I0 = orc.make_states(9, 2, 3, 48, 64, inp["Ip"])
             kw = dict(initial_mu_state=mu0.to(dev), initial_I_state=I0.to(dev), output_uncertainty=True)
-        o_ref, mu_ref, I_ref = chunk_palimpsa(*[full[n] for n in names], output_final_state=True, **kw)
-        if extras:
-            o_ref, ov_ref = o_ref
-            (o_ref.float() * inp["do"].to(dev).float()).sum().add((ov_ref.float() * inp["do_var"].to(dev).float()).sum()
-                                                                  ).backward()
-        else:
-            o_ref.backward(inp["do"].to(dev))
+        ref = orc.oracle_fwd_bwd(*[inp[n] for n in names], inp["do"], inp["do_var"] if extras else None,
+                                 mu0 if extras else None, I0 if extras else None)
         lo, hi = shard_bounds(T, rank, world)
         loc = {n: (inp[n][:, lo:hi] if inp[n].dim() >= 3 else inp[n]).to(dev).contiguous().requires_grad_(True)
                for n in names}
@@ -60,17 +54,17 @@ def _worker(rank, world, port, q_out, dtype_name, T, G, extras=False):
             o.backward(inp["do"][:, lo:hi].to(dev))
         torch.cuda.synchronize()
         tol = 1e-5 if dtype == torch.float32 else 2e-2
-        errs = {"o": orc.rel_err(o, o_ref[:, lo:hi])}
+        errs = {"o": orc.rel_err(o, ref["o"][:, lo:hi])}
         if extras:
-            errs["o_var"] = orc.rel_err(ov, ov_ref[:, lo:hi])
+            errs["o_var"] = orc.rel_err(ov, ref["o_var"][:, lo:hi])
         for n in ("q", "k", "v", "b", "gt"):
-            errs["d" + n] = orc.rel_err(loc[n].grad, full[n].grad[:, lo:hi])
-        for n in ("g", "Ip"):
-            errs["d" + n] = orc.rel_err(loc[n].grad, full[n].grad)
+            errs["d" + n] = orc.rel_err(loc[n].grad, ref["d" + n][:, lo:hi])
+        for n in ("g", "Ip"):                            # summed over the group by the op
+            errs["d" + n] = orc.rel_err(loc[n].grad, ref["d" + n])
         if rank == world - 1:
-            errs["final_mu"] = orc.rel_err(mu, mu_ref)
-            errs["final_I"] = orc.rel_err(I, I_ref)
-        bad = {n: e for n, e in errs.items() if not e <= 2 * tol}
+            errs["final_mu"] = orc.rel_err(mu, ref["final_mu"])
+            errs["final_I"] = orc.rel_err(I, ref["final_I"])
+        bad = {n: e for n, e in errs.items() if not e <= tol}
         q_out.put((rank, "ok" if not bad else "bad", errs))
         dist.barrier()
         dist.destroy_process_group()
@@ -92,8 +86,14 @@ def test_cp_matches_single_gpu(dtype_name, T, G, extras):
     procs = [ctx.Process(target=_worker, args=(r, world, port, q_out, dtype_name, T, G, extras)) for r in range(world)]
     for p in procs:
         p.start()
-    got = [q_out.get(timeout=300) for _ in range(world)]
-    for p in procs:
-        p.join(60)
+    try:
+        got = [q_out.get(timeout=300) for _ in range(world)]
+        for p in procs:
+            p.join(60)
+    finally:
+        for p in procs:                                   # a rank stuck in a receive must not outlive the test
+            if p.is_alive():
+                p.terminate()
+                p.join(10)
     for g in got:
         assert g[1] == "ok", g

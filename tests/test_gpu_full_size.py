@@ -112,3 +112,100 @@ def test_decode_configuration_matches_the_chunk_op():
             outs.append(decode_step(*[tok[n] for n in NAMES], mu, I))
     assert rel_err(torch.cat(outs, 1), o_all[:, T0:]) < 1e-2
     assert rel_err(mu, mu_all) < 1e-5 and rel_err(I, I_all) < 1e-5
+
+
+# ------------------------------------------------------------------------------------------------------------
+# The float64 oracle AT the benchmark's sizes.  The property tests above compare the CUDA path with itself; these
+# compare it with the independent CPU recurrence on whole benchmark-length sequences (one sequence and one or
+# two heads at a time is what the oracle finishes in seconds).  Bound: 2e-2 (bf16), max|x-ref| / max|ref|.
+# ------------------------------------------------------------------------------------------------------------
+from oracle import palimpsa_oracle as orc  # noqa: E402
+
+PER_TOKEN = ("dq", "dk", "dv", "db", "dgt")
+
+
+def _cpu_slice(d, seq, heads, lo=None, hi=None):
+    """Sequence ``seq``, heads ``heads`` and tokens [lo, hi) of the device dict ``d`` as CPU tensors."""
+    out = {}
+    for n, x in d.items():
+        x = x.detach().cpu()
+        if x.dim() >= 3:
+            x = x[seq:seq + 1, lo:hi][:, :, heads]
+        else:
+            x = x[heads]
+        out[n] = x
+    return out
+
+
+def _explicit(sl, **kw):
+    return orc.oracle_backward_explicit(*[sl[n] for n in NAMES], sl["do"], block=256, **kw)
+
+
+def _check(got, ref, names, what, tol=TOL_BF16):
+    errs = {n: rel_err(got[n], ref[n]) for n in names}
+    print(f"\n{what}: " + " ".join(f"{n}={e:.1e}" for n, e in errs.items()))
+    bad = {n: e for n, e in errs.items() if not e <= tol}
+    assert not bad, (what, bad)
+
+
+def test_c2_sequence_matches_the_float64_oracle(c2):
+    """One whole sequence of the 170M-shaped batch (T = 4096): outputs and final states on all 6 heads, the seven
+    gradients on two heads (dg / dIp are sums over the batch, so they come from a call on that slice alone)."""
+    d, a = c2
+    seq = 5
+    sl = _cpu_slice(d, seq, slice(0, 6))
+    with torch.no_grad():
+        o, _, mu, I = orc.oracle_forward(*[sl[n] for n in NAMES])
+    got = {"o": a["o"][seq:seq + 1], "mu": a["mu"][seq:seq + 1], "I": a["I"][seq:seq + 1]}
+    _check(got, {"o": o, "mu": mu, "I": I}, ("o", "mu", "I"), "C2 sequence, forward, 6 heads")
+    heads = slice(2, 4)
+    sl2 = _cpu_slice(d, seq, heads)
+    ref = _explicit(sl2)
+    got = {n: a[n][seq:seq + 1][:, :, heads] for n in PER_TOKEN}
+    got["o"] = a["o"][seq:seq + 1][:, :, heads]
+    _check(got, ref, ("o",) + PER_TOKEN, "C2 sequence, gradients, heads 2-3")
+    alone = _fwd_bwd({n: x.to(DEV) for n, x in sl2.items()})
+    _check(alone, ref, ("dg", "dIp") + PER_TOKEN, "C2 sequence alone (parameter gradients)")
+
+
+def test_packed_batch_documents_match_the_float64_oracle():
+    """The packed training batch (32 768 tokens, documents of seeded random length in [128, 4096], states reset at
+    every boundary): the longest and the shortest document against the oracle run on that document alone."""
+    T, H = 32768, 6
+    gen = torch.Generator().manual_seed(0)
+    lens, tot = [], 0
+    while tot < T:
+        n = min(int(torch.randint(128, 4097, (1,), generator=gen).item()), T - tot)
+        lens.append(n)
+        tot += n
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    d = _inputs(1, T, H, 128, 128, seed=0)
+    a = _fwd_bwd(d, cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=DEV))
+    order = sorted(range(len(lens)), key=lambda i: lens[i])
+    heads = slice(0, 2)
+    for doc in (order[-1], order[0]):
+        lo, hi = cu[doc], cu[doc + 1]
+        ref = _explicit(_cpu_slice(d, 0, heads, lo, hi))
+        got = {n: a[n][:, lo:hi][:, :, heads] for n in ("o",) + PER_TOKEN}
+        got["final_mu"], got["final_I"] = a["mu"][doc:doc + 1, heads], a["I"][doc:doc + 1, heads]
+        _check(got, ref, ("o", "final_mu", "final_I") + PER_TOKEN, f"packed batch, document {doc} ({hi - lo} tokens)")
+
+
+def test_long_segmented_sequence_matches_the_float64_oracle():
+    """One 32 768-token sequence cut into 32 segments (tensor-core summaries, boundary scans, carried-gradient
+    terms): every token's output and gradients, the final state and the parameter gradients of one head against a
+    float64 walk of the whole sequence (which also supplies the true boundary states and carried gradients)."""
+    d = _inputs(1, 32768, 2, 128, 128, seed=11)
+    d["gt"] = d["gt"] * 0.05                         # slow decay: early tokens reach the end of the sequence
+    a = _fwd_bwd(d, num_segments=32)
+    head = slice(1, 2)
+    ref = _explicit(_cpu_slice(d, 0, head))
+    got = {n: a[n][:, :, head] for n in ("o",) + PER_TOKEN}
+    got.update(final_mu=a["mu"][:, head], final_I=a["I"][:, head], dg=a["dg"][head], dIp=a["dIp"][head])
+    names = ("o", "final_mu", "final_I", "dg", "dIp") + PER_TOKEN
+    _check(got, ref, names, "32 segments x 1024 tokens, all tokens")
+    for lo, hi, tag in ((0, 2048, "first"), (32768 - 2048, 32768, "last")):
+        win = {n: got[n][:, lo:hi] for n in ("o",) + PER_TOKEN}
+        _check(win, {n: ref[n][:, lo:hi] for n in win}, tuple(win), f"{tag} 2048 tokens")

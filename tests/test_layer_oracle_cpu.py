@@ -39,3 +39,27 @@ def test_oracle_gradients_by_finite_differences():
     assert torch.autograd.gradcheck(lambda *a: lo.layer_prologue_ref(*a), args, eps=1e-6, atol=1e-6)
     eargs = [d[n].double().requires_grad_(True) for n in ("o", "x", "D", "weight", "gate")]
     assert torch.autograd.gradcheck(lambda *a: lo.layer_epilogue_ref(*a), eargs, eps=1e-6, atol=1e-6)
+
+
+def test_epilogue_oracle_against_the_gated_norm_fixture():
+    """The fixture holds outputs and gradients of flash-linear-attention's own FusedRMSNormGated (generated on a GPU
+    by tests/golden/make_gated_norm_golden.py); the oracle's restatement must reproduce them."""
+    import os
+
+    import numpy as np
+    import pytest
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "gated_norm.npz")
+    if not os.path.exists(path):
+        pytest.skip("tests/golden/gated_norm.npz has not been generated yet")
+    z = np.load(path)
+    eps = float(z["meta_eps"])
+    for tag, tol in (("f32", 2e-6), ("f32_v48", 2e-6), ("bf16", 1e-2)):
+        zz = torch.from_numpy(z[f"{tag}_z"]).double().requires_grad_(True)
+        gate = torch.from_numpy(z[f"{tag}_gate"]).double().requires_grad_(True)
+        w = torch.from_numpy(z[f"{tag}_weight"]).double().requires_grad_(True)
+        y = lo.layer_epilogue_ref(zz, None, None, w, gate, eps)
+        y.backward(torch.from_numpy(z[f"{tag}_dy"]).double())
+        for name, got in (("y", y.detach()), ("dz", zz.grad), ("dgate", gate.grad), ("dweight", w.grad)):
+            ref = torch.from_numpy(z[f"{tag}_{name}"]).double()
+            err = (got - ref).abs().max().item() / ref.abs().max().item()
+            assert err <= tol, (tag, name, err)
