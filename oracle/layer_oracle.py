@@ -13,8 +13,10 @@ Gradients come from autograd through these expressions.  ``compute`` is the dtyp
 (float64 for the exact answer; pass the activation dtype itself to get the layer's own rounding points).
 
 Parity pin: the prologue is made of the same torch functions, in the same order, as the layer's lines and
-needs no further pin.  The gated norm is "parity unpinned": its reference is a Triton kernel that cannot run
-on a CPU, so the epilogue oracle follows the published formula only.
+needs no further pin.  The gated norm is pinned against flash-linear-attention's own ``FusedRMSNormGated``:
+``tests/golden/gated_norm.npz`` holds that module's outputs and gradients (float32 and bfloat16), generated on a
+GPU by ``tests/golden/make_gated_norm_golden.py`` (its kernels are Triton and cannot run on a CPU), and
+``tests/test_layer_oracle_cpu.py`` checks this restatement against the file.
 
 Only the tests may import this module.
 """

@@ -90,6 +90,7 @@ def sm_count(device=None) -> int:
     return _sm_count_cache[idx]
 
 
+@torch.compiler.assume_constant_result        # ints in, int out: evaluated once when a caller is traced by torch.compile
 def plan_segments(N: int, T: int, H: int, K: int, V: int, device=None) -> int:
     """How many segments to cut every sequence into on one GPU.  Segments cost an extra summary pass
     (and the carried-gradient terms in backward), so they are only used when the (sequence, head,

@@ -31,7 +31,7 @@ def main():
     dev = torch.device("cuda", 0)
     arrs = {"meta_fla_version": np.array(fla.__version__), "meta_eps": np.array(1e-5)}
     for tag, dtype, V in (("f32", torch.float32, 128), ("bf16", torch.bfloat16, 128), ("f32_v48", torch.float32, 48)):
-        d = make_layer_inputs(11, B=2, T=37, H=3, Hq=3, K=8, V=V, dtype=dtype)
+        d = make_layer_inputs(11, B=1, T=13, H=3, Hq=3, K=8, V=V, dtype=dtype)
         norm = FusedRMSNormGated(V, eps=1e-5).to(dev)
         with torch.no_grad():
             norm.weight.copy_(d["weight"].to(dev))
