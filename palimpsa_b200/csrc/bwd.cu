@@ -10,15 +10,9 @@
 //      tokens in reverse, carrying the state gradients (GM, -GI) in registers:
 //          h    = dy*q_s / I            GM = f_next*GM + h          -GI = f_next*(-GI) + h*mu (+var)
 //          dq  += dy*mu   dk += GM*v + 2k*GI*b   dv += GM*k   db += GI*k^2
-//      (the algebra of chunk_palimpsa_bwd_kernel, chunk_palimpsa_forgetting_scalar.py:343-434).
-//      The decay gradient needs f_t*df_t = <GM_t, f_t M_{t-1}> + <GI_t, f_t (I_{t-1} - Ip)>.  The reference
-//      rebuilds M_{t-1} by a division (:409-410); here no previous state is touched at all:
-//      f_t M_{t-1} = M_t - v_t k_t^T and f_t (I_{t-1} - Ip) = J_t - b_t (k_t^2)^T with J = I - Ip, hence
-//          f_t df_t = A_t - c_t,   A_t = <GM_t, M_t> + <GI_t, J_t>,   c_t = <v_t, dv_t> + <b_t, db_t>,
-//      and A obeys A_t = A_{t+1} - c_{t+1} + Ip*s_t - u_t with the per-token scalars s_t = sum(h*mu [+ var]) and
-//      u_t = <dy_var, o_var> (0 without the uncertainty output).  Per state element that is ONE add (s_t)
-//      instead of two FMAs; A is re-anchored from registers at the last token of every 16-token block, so
-//      rounding does not accumulate along the sequence.
+//          df   = <GM, M_prev> + <GI, I_prev - Ip>
+//      (the algebra of chunk_palimpsa_bwd_kernel, chunk_palimpsa_forgetting_scalar.py:343-434,
+//      with the previous state carried forward instead of rebuilt by a division, :409-410).
 // Reductions: over d_k (dv, db) by xor-shuffles inside the lanes of a row; over d_v (dq, dk) first
 // in registers across a thread's rows, then across the CTA's row groups through shared memory, and
 // across the CTAs of different row tiles through fp32 partial buffers in the workspace, which the
@@ -28,7 +22,7 @@
 // One CTA per SM: 11 or 12 warps at d_k = 128 (22- or 24-row tiles, whichever pads d_v less).
 //
 // Finishing kernels: (1) per (token, head) row: sum the row tiles, cast dq/dk, form
-// dgt = -g (f df) and the per-row terms of dg and dIp; (2) per head: ordered sum over rows.
+// dgt = -g f df and the per-row terms of dg and dIp; (2) per head: ordered sum over rows.
 #include <mutex>
 
 #include "host.h"
@@ -101,7 +95,7 @@ __host__ __device__ inline BwdSmem bwd_smem_layout(int KP, int TV, int NE, int n
     s.fn2 = take(TB * 8);
     s.dvs = take(TB * TV * 4);
     s.dbs = take(TB * TV * 4);
-    s.wred = take((nthr / 32) * (TB * 2 + 2) * 4);   // per warp: (s_t, u_t) per token, then the anchor and the start sum
+    s.wred = take((nthr / 32) * TB * 2 * 4);
     s.slots = take(2 * 2 * NE * nthr * 4);
     s.ck_stage = 2 * TV * KP * 4;
     s.ckb = take(2 * s.ck_stage);
@@ -305,9 +299,7 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
     constexpr int TV = W * VG * RV, WV = W * VG, NTHR = 32 * W;
     constexpr int NG = TB / GR;       // groups per block
     constexpr int NR1 = GR * RV * 2;  // per-group d_v-indexed partials of a thread: (token, row, dv|db)
-    constexpr int NRS = UNC ? 2 : 1;  // per-token scalars of a thread: s_t (and u_t with the uncertainty output)
-    constexpr int NR2 = GR * NRS;
-    constexpr int WSTRIDE = TB * 2 + 2;  // floats per warp in wred
+    constexpr int NR2 = GR * 2;       // per-group per-token scalars: (token, df|sum GI)
     extern __shared__ __align__(16) unsigned char sm[];
     const palimpsa_problem& p = a.p;
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
@@ -403,21 +395,6 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                 nGI[r][q] = make_float2(-ci.x, -ci.y);
             }
         }
-
-    // sum of -dL/dI over this CTA's state elements at the segment's end (the end-state gradient, if one is given):
-    // start value of the running total that the prior-precision gradient needs
-    if (!CO) {
-        float2 t2 = make_float2(0.f, 0.f);
-#pragma unroll
-        for (int r = 0; r < RV; ++r)
-#pragma unroll
-            for (int q = 0; q < NP; ++q) t2 = fadd2(t2, nGI[r][q]);
-        float t1 = t2.x + t2.y;
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) t1 += __shfl_xor_sync(0xffffffffu, t1, off);
-        if (lane == 0) wred[w * WSTRIDE + TB * 2 + 1] = t1;
-    }
-    float sn_next = 0.f;  // warp 0: sum of -dL/dI_{t+1} over the CTA's elements, t+1 = first token after the block
 
     auto load_ck = [&](State<RV, NP>& s, int stage_idx) {
         const float* ckM = reinterpret_cast<const float*>(sm + L.ckb + stage_idx * L.ck_stage);
@@ -573,9 +550,9 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                 const int tl = gi * GR + j;
                 const float2 fn = fn2[tl];
                 float2 dqs[NP], Ak[NP], Bk[NP], Uk[NP];
-                float2 Ss[RV];  // s_t = sum of the local -dL/dI terms; one accumulator per row: shorter chains
+                float2 Sa[RV], Sb[RV], Sc[RV];  // one accumulator per row: shorter dependent chains
 #pragma unroll
-                for (int r = 0; r < RV; ++r) Ss[r] = make_float2(0.f, 0.f);
+                for (int r = 0; r < RV; ++r) Sa[r] = Sb[r] = Sc[r] = make_float2(0.f, 0.f);
 #pragma unroll
                 for (int q = 0; q < NP; ++q) dqs[q] = Ak[q] = Bk[q] = Uk[q] = make_float2(0.f, 0.f);
                 float2 kp[NP], kk[NP], qp[NP], qq[NP];
@@ -612,13 +589,15 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                         if (UNC) hm = ffma2(fmul2(dyv, qq[q]), fmul2(rr, rr), hm);
                         nGI[r][q] = ffma2(fn, nGI[r][q], hm);
                         if (!CO) {
-                            Ss[r] = fadd2(Ss[r], hm);
                             dqs[q] = ffma2(dy, mu, dqs[q]);
                             if (UNC) Uk[q] = ffma2(dyv, rr, Uk[q]);
                             Ak[q] = ffma2(GM[r][q], vv, Ak[q]);
                             Bk[q] = ffma2(nGI[r][q], bv, Bk[q]);
                             dva = ffma2(GM[r][q], kp[q], dva);
                             dba = ffma2(nGI[r][q], kk[q], dba);
+                            Sa[r] = ffma2(GM[r][q], P[j].M[r][q], Sa[r]);
+                            Sb[r] = ffma2(nGI[r][q], P[j].I[r][q], Sb[r]);
+                            Sc[r] = fadd2(Sc[r], nGI[r][q]);
                         }
                     }
                     red1[(j * RV + r) * 2 + 0] = dva.x + dva.y;
@@ -632,56 +611,24 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                 if (!CO) {
                     float2* dst = kred2 + (gi & (KBUF - 1)) * (GR * WV * 2 * KP2) + ((j * WV + wv) * 2) * KP2 + NP * kg;
                     const float2 sc2 = dup2(p.scale), m2 = dup2(-2.f);
-                    float2 dqv[NP], dkv[NP];
 #pragma unroll
                     for (int q = 0; q < NP; ++q) {
-                        dqv[q] = fmul2(sc2, dqs[q]);
-                        if (UNC) dqv[q] = ffma2(fmul2(dup2(2.f), qp[q]), Uk[q], dqv[q]);
-                        dkv[q] = ffma2(fmul2(m2, kp[q]), Bk[q], Ak[q]);
-                    }
-                    if constexpr (NP % 2 == 0) {  // two adjacent pairs leave as one 16-byte store
-#pragma unroll
-                        for (int q = 0; q < NP; q += 2) {
-                            *reinterpret_cast<float4*>(dst + q) = make_float4(dqv[q].x, dqv[q].y, dqv[q + 1].x, dqv[q + 1].y);
-                            *reinterpret_cast<float4*>(dst + KP2 + q) =
-                                make_float4(dkv[q].x, dkv[q].y, dkv[q + 1].x, dkv[q + 1].y);
-                        }
-                    } else {
-#pragma unroll
-                        for (int q = 0; q < NP; ++q) {
-                            dst[q] = dqv[q];
-                            dst[KP2 + q] = dkv[q];
-                        }
+                        float2 dqv = fmul2(sc2, dqs[q]);
+                        if (UNC) dqv = ffma2(fmul2(dup2(2.f), qp[q]), Uk[q], dqv);
+                        dst[q] = dqv;
+                        dst[KP2 + q] = ffma2(fmul2(m2, kp[q]), Bk[q], Ak[q]);
                     }
                 }
-                if (!CO) {
-                    float2 ss = Ss[0];
+                float2 sa = Sa[0], sb = Sb[0], scv = Sc[0];
 #pragma unroll
-                    for (int r = 1; r < RV; ++r) ss = fadd2(ss, Ss[r]);
-                    red2[j * NRS] = ss.x + ss.y;
-                    if (UNC) {  // u_t = sum_{v,k} dy_var * scale q^2 / I = <dy_var_t, o_var_t> over this thread's elements
-                        float2 uu = make_float2(0.f, 0.f);
-#pragma unroll
-                        for (int q = 0; q < NP; ++q) uu = ffma2(qq[q], Uk[q], uu);
-                        red2[j * NRS + NRS - 1] = uu.x + uu.y;
-                    }
-                    // anchor of the decay-gradient recurrence: A = <GM, M> + <GI, I - Ip> at the block's last token slot
-                    if (j == GR - 1 && gi == NG - 1) {
-                        float2 am = make_float2(0.f, 0.f), ai = am;
-                        const float2 nip = dup2(-iph);
-#pragma unroll
-                        for (int r = 0; r < RV; ++r)
-#pragma unroll
-                            for (int q = 0; q < NP; ++q) {
-                                am = ffma2(GM[r][q], P[GR].M[r][q], am);
-                                ai = ffma2(nGI[r][q], fadd2(P[GR].I[r][q], nip), ai);
-                            }
-                        float an = (am.x + am.y) - (ai.x + ai.y);
-#pragma unroll
-                        for (int off = 16; off >= 1; off >>= 1) an += __shfl_xor_sync(0xffffffffu, an, off);
-                        if (lane == 0) wred[w * WSTRIDE + TB * 2] = an;
-                    }
+                for (int r = 1; r < RV; ++r) {
+                    sa = fadd2(sa, Sa[r]);
+                    sb = fadd2(sb, Sb[r]);
+                    scv = fadd2(scv, Sc[r]);
                 }
+                const float sc_ = scv.x + scv.y;
+                red2[j * 2 + 0] = (sa.x + sa.y) - (sb.x + sb.y) + iph * sc_;
+                red2[j * 2 + 1] = -sc_;
             }
             if (CO) continue;  // carry-only pass: nothing but the state gradients is wanted
             __syncwarp();
@@ -704,51 +651,24 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
             xreduce<NR2, 32>(red2, lane);
             if ((lane & (32 / NR2 - 1)) == 0) {
                 const int id = xreduce_index<NR2, 32>(lane);
-                wred[w * WSTRIDE + (gi * GR + id / NRS) * 2 + (id % NRS)] = red2[0];
+                wred[(w * TB + gi * GR + (id >> 1)) * 2 + (id & 1)] = red2[0];
             }
             if (!wait_fail && !tc::mbar_wait(&gbar[0], ph_a)) wait_fail = 5;
             ph_a ^= 1;
             // ---- sum the row groups' shares; emit this row tile's dq / dk partials ----------------------
             const int ng = min(GR, nt - gi * GR);  // tokens of the group that exist (<= 0 past the sequence end)
-            // 16-byte column groups; the WV row-group shares of a column group are split between lane l and lane
-            // l ^ 16 of a warp (the 16 lanes of a half read 256 contiguous bytes), which then exchange their halves:
-            // the lower lane stores dq, the upper one dk (fixed order of additions: bitwise reproducible)
-            constexpr int KP4 = KP / 4, WH = (WV + 1) / 2;
-            const int items = ng * KP4;
-            const int half = lane >> 4;
-            for (int base = 0; base < items; base += W * 16) {
-                const int ci0 = base + w * 16 + (lane & 15);
-                const bool act = ci0 < items;
-                const int ci = act ? ci0 : 0;
-                const int j = ci / KP4, pi = ci - j * KP4;
-                const float4* src = reinterpret_cast<const float4*>(kred2 + (gi & (KBUF - 1)) * (GR * WV * 2 * KP2) +
-                                                                    (j * WV * 2) * KP2) + pi;
-                float2 q0 = make_float2(0.f, 0.f), q1 = q0, k0 = q0, k1 = q0;
+            for (int i = tid; i < ng * KP2; i += NTHR) {
+                const int j = i / KP2, pi = i - j * KP2;
+                const float2* src = kred2 + (gi & (KBUF - 1)) * (GR * WV * 2 * KP2) + (j * WV * 2) * KP2 + pi;
+                float2 s0 = make_float2(0.f, 0.f), s1 = s0;
 #pragma unroll
-                for (int xx = 0; xx < WH; ++xx) {
-                    const int x = half * WH + xx;
-                    if (x < WV) {
-                        const float4 a4 = src[(x * 2) * KP4], b4 = src[(x * 2 + 1) * KP4];
-                        q0 = fadd2(q0, make_float2(a4.x, a4.y));
-                        q1 = fadd2(q1, make_float2(a4.z, a4.w));
-                        k0 = fadd2(k0, make_float2(b4.x, b4.y));
-                        k1 = fadd2(k1, make_float2(b4.z, b4.w));
-                    }
+                for (int x = 0; x < WV; ++x) {
+                    s0 = fadd2(s0, src[(x * 2) * KP2]);
+                    s1 = fadd2(s1, src[(x * 2 + 1) * KP2]);
                 }
-                // the lower lane needs the partner's dq half, the upper lane the partner's dk half
-                const float2 s0 = half ? q0 : k0, s1 = half ? q1 : k1;          // what the partner wants from me
-                float2 r0, r1;
-                r0.x = __shfl_xor_sync(0xffffffffu, s0.x, 16);
-                r0.y = __shfl_xor_sync(0xffffffffu, s0.y, 16);
-                r1.x = __shfl_xor_sync(0xffffffffu, s1.x, 16);
-                r1.y = __shfl_xor_sync(0xffffffffu, s1.y, 16);
-                if (act) {
-                    const float2 m0 = half ? k0 : q0, m1 = half ? k1 : q1;       // my own share of what I store
-                    const float2 o0 = fadd2(m0, r0), o1 = fadd2(m1, r1);
-                    const size_t e = (((size_t)tile * a.rows_total + (size_t)(tok0 + gi * GR + j) * p.H + h) * KP4) + pi;
-                    float4* dstp = reinterpret_cast<float4*>(half ? a.dk_part : a.dq_part);
-                    dstp[e] = make_float4(o0.x, o0.y, o1.x, o1.y);
-                }
+                const size_t e = (((size_t)tile * a.rows_total + (size_t)(tok0 + gi * GR + j) * p.H + h) * KP2) + pi;
+                reinterpret_cast<float2*>(a.dq_part)[e] = s0;
+                reinterpret_cast<float2*>(a.dk_part)[e] = s1;
             }
             // with two buffers no second barrier is needed: the next group writes the other buffer, and the
             // barrier after ITS reverse walk orders this group's reads before the buffer is reused
@@ -769,51 +689,19 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
                 st1(a.db, e, dbs[i], p.io_dtype);
             }
         }
-        if (w == 0) {
-            // Per-token scalars of the block, token t on lane t (lanes 16..31 mirror them):
-            //   s_t, u_t from the warps' partials;  c_t = <v_t, dv_t> + <b_t, db_t> from the rows just reduced;
-            //   A_t = A_15 + sum_{u=t}^{14} (Ip s_u - u_u - c_{u+1})   (suffix sum from the anchor);  f_t df_t = A_t - c_t;
-            //   n_t = s_t + fn_t n_{t+1}: running sum of -dL/dI over the elements (affine suffix scan), for dIp.
-            const int t = lane & (TB - 1);
-            float s = 0.f, u = 0.f, anchor = 0.f;
+        if (tid < nt) {
+            float df = 0.f, s2 = 0.f;
 #pragma unroll
             for (int x = 0; x < W; ++x) {
-                s += wred[x * WSTRIDE + t * 2];
-                if (UNC) u += wred[x * WSTRIDE + t * 2 + 1];
-                anchor += wred[x * WSTRIDE + TB * 2];
-                if (it == 0) sn_next += wred[x * WSTRIDE + TB * 2 + 1];
+                df += wred[(x * TB + tid) * 2 + 0];
+                s2 += wred[(x * TB + tid) * 2 + 1];
             }
-            const float2* vrow = reinterpret_cast<const float2*>(sm + L.vs2) + t * TV;
-            const float2* brow = reinterpret_cast<const float2*>(sm + L.bs2) + t * TV;
-            float c = 0.f;  // two lanes per token: rows [0, TVH) on lanes 0..15, [TVH, TV) on lanes 16..31
-            constexpr int TVH = (TV + 1) / 2;
-            for (int r = (lane >> 4) * TVH; r < min(TV, ((lane >> 4) + 1) * TVH); ++r)
-                c = fmaf(vrow[r].x, dvs[t * TV + r], fmaf(brow[r].x, dbs[t * TV + r], c));
-            c += __shfl_xor_sync(0xffffffffu, c, 16);
-            const float c_up = __shfl_down_sync(0xffffffffu, c, 1);            // c_{t+1}
-            float e = t < TB - 1 ? fmaf(iph, s, -u) - c_up : 0.f;
-            float F = fn2[t].x, Wn = s;
-#pragma unroll
-            for (int off = 1; off < TB; off <<= 1) {
-                const float eo = __shfl_down_sync(0xffffffffu, e, off);
-                const float Fo = __shfl_down_sync(0xffffffffu, F, off), Wo = __shfl_down_sync(0xffffffffu, Wn, off);
-                if (t + off < TB) {
-                    e += eo;
-                    Wn = fmaf(F, Wo, Wn);
-                    F *= Fo;
-                }
-            }
-            const float fdf = anchor + e - c;
-            const float n_t = fmaf(F, sn_next, Wn);
-            sn_next = __shfl_sync(0xffffffffu, n_t, 0);
-            if (lane < nt) {
-                const float f = fc2[t].x;
-                float dip = (f - 1.f) * n_t;                       // (1 - f_t) * sum dL/dI_t
-                if (t0 + t == 0 && !has_init) dip -= f * n_t;      // I_0 = Ip: the start-state gradient reaches Ip
-                const size_t eo = (size_t)tile * a.rows_total + (size_t)(tok0 + t) * p.H + h;
-                a.df_part[eo] = fdf;
-                a.dip_part[eo] = dip;
-            }
+            const float f = fc2[tid].x;
+            float dip = (1.f - f) * s2;
+            if (t0 + tid == 0 && !has_init) dip += f * s2;  // I_0 = Ip: the start-state gradient reaches Ip
+            const size_t e = (size_t)tile * a.rows_total + (size_t)(tok0 + tid) * p.H + h;
+            a.df_part[e] = df;
+            a.dip_part[e] = dip;
         }
         // the next iteration's first barrier orders these reads before the buffers are reused
     }
@@ -909,8 +797,9 @@ __global__ void __launch_bounds__(256) bwd_finish_rows(const palimpsa_problem p,
         dip += __shfl_xor_sync(0xffffffffu, dip, off);
     }
     if (lane == 0) {
-        dgt[row] = -gh * df;    // df holds f_t * dL/df_t
-        w_dg[row] = -gtv * df;
+        const float f = expf(-gtv * gh);
+        dgt[row] = -gh * f * df;
+        w_dg[row] = -gtv * f * df;
         w_dip[row] = dip;
     }
 }

@@ -6,7 +6,6 @@
 //     dv_t += a_t (R_M k_t)            db_t += a_t (R_I k_t^2)
 //     dk_t += a_t (R_M^T v_t + 2 k_t * (R_I^T b_t))
 //     df_t += a_t c_t ,  c_{t+1} = f_t c_t + <R_M^T v_t, k_t> + <R_I^T b_t, k_t^2>,  c_first = <R_M, M_start> + <R_I, J_start>
-//     (stored as f_t df_t, like the main kernel's partials)
 //     sum(GI_t) += a_t sum(R_I)        (enters dIp)
 // i.e. four [tokens x 128]*[128 x 128] products per segment plus per-token scalar work.  One CTA per
 // (sequence, head, segment) keeps R (bf16, both orientations) resident in shared memory as UMMA B
@@ -310,8 +309,7 @@ __global__ void __launch_bounds__(128) carry_tc_kernel(const CarryArgs a) {
         const float c_t = lane == 0 ? c_ws : fmaf(Fp, c_ws, Wp);
         if (tid == 127) cnext_s = fmaf(F, c_ws, Wc);
         if (live) {
-            // the partial slots hold f_t * dL/df_t (what dgt and dg are made of); NaN if a wait ran out
-            a.df_x[row] = status == 0 ? f_t * a_t * c_t : __int_as_float(0x7fc00000);
+            a.df_x[row] = status == 0 ? a_t * c_t : __int_as_float(0x7fc00000);  // a wait ran out: mark dgt / dg invalid
             float dip = (1.f - f_t) * a_t * SRI;
             if (t0 + tid == 0 && !has_init) dip += f_t * a_t * SRI;
             a.dip_x[row] = dip;
