@@ -9,8 +9,12 @@
 //     sum(GI_t) += a_t sum(R_I)        (enters dIp)
 // i.e. four [tokens x 128]*[128 x 128] products per segment plus per-token scalar work.  One CTA per
 // (sequence, head, segment) keeps R (bf16, both orientations) resident in shared memory as UMMA B
-// operands and walks the segment in 128-token tiles: the token rows of k, k^2, v, b are copied into the
-// K-major core-matrix layout as A operands (each thread copies its own token row), one thread issues the
+// operands and walks the segment in 128-token tiles.  The token rows of k, v and b are A operands exactly as they
+// lie in global memory (token-major, contraction dimension contiguous = K-major), so where the head dimensions
+// allow it (d_k, d_v multiples of 64) they arrive by TMA: cp.async.bulk.tensor 2-D tiles of 128 tokens x 64
+// elements with the 128-byte swizzle, completion on an mbarrier (complete_tx), descriptors in the matching
+// swizzled layout; only k^2 is produced in registers (each thread squares its own token row into the unswizzled
+// core-matrix layout).  Other shapes copy all four row sets by hand.  One thread issues the
 // tcgen05.mma's into four TMEM accumulators, and every thread reads back the TMEM lane of its token and
 // applies the result (read-modify-write of dv, db; dk / df / dIp terms into the extra partial slot the
 // finishing kernels sum).  All waits are bounded.  The reference has no counterpart: it never splits a
@@ -24,6 +28,9 @@ constexpr int CT = 128;                    // tokens per tile = UMMA M
 constexpr int C_LBO = 128;                 // bytes between K-direction core matrices
 constexpr int C_SBO = 16 * 128 + 16;       // bytes between 8-row groups (K extent <= 128; padded against bank conflicts)
 constexpr int C_OPER = 16 * C_SBO;         // one 128-row operand
+constexpr int C_BOX = 128 * 128;           // one TMA box: 128 token rows x 64 bf16 (128 bytes), swizzled
+constexpr int C_A0 = 2 * C_BOX;            // A0: up to two boxes side by side (contraction extent <= 128)
+constexpr int C_A1 = (C_OPER + 1023) / 1024 * 1024;   // A1: by hand (k^2, unswizzled) or by TMA (b rows)
 constexpr int C_MAXTILES = 1024;           // segment length limit: 131 072 tokens
 
 __device__ int g_carry_status = 0;         // 0 ok; 3 / 4: the bounded wait after phase 1 / phase 2 gave up
@@ -38,13 +45,21 @@ struct CarryArgs {
     int KP, VP;
 };
 
+struct CarryMaps {                         // tensor maps over this GPU's k, v, b: rows = tokens, row = H * d elements
+    CUtensorMap k, v, b;
+};
+
 __device__ __forceinline__ unsigned char* core_addr(unsigned char* base, int row, int chunk) {
     return base + (row >> 3) * C_SBO + chunk * 128 + (row & 7) * 16;
 }
 
-__global__ void __launch_bounds__(128) carry_tc_kernel(const CarryArgs a) {
-    extern __shared__ __align__(128) unsigned char sm[];
+template <bool TMA>
+__global__ void __launch_bounds__(128) carry_tc_kernel(const CarryArgs a, const __grid_constant__ CarryMaps maps) {
+    extern __shared__ __align__(128) unsigned char sm_raw[];
+    // the TMA destinations want 1024-byte alignment (swizzle atom): round the dynamic base up
+    unsigned char* sm = sm_raw + ((1024u - (tc::smem_u32(sm_raw) & 1023u)) & 1023u);
     __shared__ __align__(8) unsigned long long bars[2];
+    __shared__ __align__(8) unsigned long long tbar;   // completion of the TMA tile loads
     __shared__ unsigned tmem_slot;
     __shared__ float tail_s[C_MAXTILES];
     __shared__ float lf_s[CT];
@@ -64,21 +79,28 @@ __global__ void __launch_bounds__(128) carry_tc_kernel(const CarryArgs a) {
     const float gh = p.g[h], iph = p.Ip[h];
     const long long seg_row = (((long long)n * G + g) * H + h) * V;
     const bool has_init = p.init_mu != nullptr || (p.flags & PALIMPSA_FLAG_EXPLICIT_INIT);
-    unsigned char* B_RM = sm;                  // rows v, K = k      (for X = K R_M^T)
-    unsigned char* B_RI = sm + C_OPER;
-    unsigned char* B_RMt = sm + 2 * C_OPER;    // rows k, K = v      (for U = V R_M)
-    unsigned char* B_RIt = sm + 3 * C_OPER;
-    unsigned char* A0 = sm + 4 * C_OPER;
-    unsigned char* A1 = sm + 5 * C_OPER;
+    unsigned char* A0 = sm;                    // 1024-byte aligned: TMA destination (k rows, then v rows)
+    unsigned char* A1 = sm + C_A0;             // 1024-byte aligned: k^2 by hand, then b rows by TMA
+    unsigned char* B_RM = sm + C_A0 + C_A1;    // rows v, K = k      (for X = K R_M^T)
+    unsigned char* B_RI = B_RM + C_OPER;
+    unsigned char* B_RMt = B_RM + 2 * C_OPER;  // rows k, K = v      (for U = V R_M)
+    unsigned char* B_RIt = B_RM + 3 * C_OPER;
 
     if (tid == 0) {
         tc::mbar_init(&bars[0]);
         tc::mbar_init(&bars[1]);
+        tc::mbar_init(&tbar);
         tc::mbar_init_fence();
+        if (TMA) {
+            tc::tma_prefetch_map(&maps.k);
+            tc::tma_prefetch_map(&maps.v);
+            tc::tma_prefetch_map(&maps.b);
+        }
     }
     if (w == 0) tc::tmem_alloc(&tmem_slot, 512);
     // ---- B operands: R in bf16, both orientations; zero everything first (padding rows / columns) ----
-    for (int i = tid; i < 6 * C_OPER / 16; i += 128) reinterpret_cast<uint4*>(sm)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < (C_A0 + C_A1 + 4 * C_OPER) / 16; i += 128) reinterpret_cast<uint4*>(sm)[i] = make_uint4(0, 0, 0, 0);
+    tc::fence_async_smem();   // these plain stores are ordered before the TMA writes into the same buffers
     __syncthreads();
     float c0 = 0.f, sri = 0.f;
     {
@@ -155,6 +177,7 @@ __global__ void __launch_bounds__(128) carry_tc_kernel(const CarryArgs a) {
     const unsigned idesc_v = tc::idesc_bf16(VP), idesc_k = tc::idesc_bf16(KP);
     const unsigned lane_base = (unsigned)(32 * w) << 16;
     int status = 0;
+    unsigned tpar = 0;                     // thread 0: parity of the next completion of tbar
     const __nv_bfloat16* gk = reinterpret_cast<const __nv_bfloat16*>(p.k);
     const __nv_bfloat16* gv = reinterpret_cast<const __nv_bfloat16*>(p.v);
     const __nv_bfloat16* gb = reinterpret_cast<const __nv_bfloat16*>(p.b);
@@ -175,11 +198,16 @@ __global__ void __launch_bounds__(128) carry_tc_kernel(const CarryArgs a) {
         const float f_t = __expf(lf);
         const float a_t = live ? __expf(sfx) : 0.f;
 
-        // ---- phase 1 operands: A0 = k rows, A1 = k*k rows (each thread copies its own token row) ----
+        // ---- phase 1 operands: A0 = k rows (TMA, or copied by hand), A1 = k*k rows (each thread squares its own row) ----
+        if (TMA && tid == 0 && status == 0) {
+            tc::mbar_expect_tx(&tbar, (unsigned)(KP / 64) * C_BOX);
+            for (int i = 0; i < KP / 64; ++i)
+                tc::tma_load_2d(A0 + i * C_BOX, &maps.k, h * K + 64 * i, (int)(bos + t0), &tbar);
+        }
         for (int c = 0; c < KP / 8; ++c) {
             uint4 x = make_uint4(0, 0, 0, 0);
             if (live && 8 * c < K) x = *reinterpret_cast<const uint4*>(gk + row * K + 8 * c);
-            *reinterpret_cast<uint4*>(core_addr(A0, tid, c)) = x;
+            if (!TMA) *reinterpret_cast<uint4*>(core_addr(A0, tid, c)) = x;
             const unsigned u[4] = {x.x, x.y, x.z, x.w};
             unsigned sq[4];
 #pragma unroll
@@ -194,9 +222,18 @@ __global__ void __launch_bounds__(128) carry_tc_kernel(const CarryArgs a) {
         __syncthreads();
         if (tid == 0 && status == 0) {
             tc::fence_after_sync();
+            if (TMA) {
+                if (!tc::mbar_wait(&tbar, tpar)) status = 3;
+                tpar ^= 1;
+            }
+        }
+        if (tid == 0 && status == 0) {
             const unsigned a0 = tc::smem_u32(A0), a1 = tc::smem_u32(A1), brm = tc::smem_u32(B_RM), bri = tc::smem_u32(B_RI);
             for (int kk = 0; kk < KP / 16; ++kk) {
-                tc::mma(tmem + 0, tc::desc(a0 + kk * 256, C_LBO, C_SBO), tc::desc(brm + kk * 256, C_LBO, C_SBO), idesc_v, kk > 0);
+                // a swizzled box holds 4 steps of K = 16 (32 bytes each); the next box is C_BOX further
+                const unsigned long long dA0 = TMA ? tc::desc_sw128(a0 + (kk >> 2) * C_BOX + (kk & 3) * 32)
+                                                   : tc::desc(a0 + kk * 256, C_LBO, C_SBO);
+                tc::mma(tmem + 0, dA0, tc::desc(brm + kk * 256, C_LBO, C_SBO), idesc_v, kk > 0);
                 tc::mma(tmem + 128, tc::desc(a1 + kk * 256, C_LBO, C_SBO), tc::desc(bri + kk * 256, C_LBO, C_SBO), idesc_v, kk > 0);
             }
             tc::commit(&bars[0]);
@@ -204,24 +241,43 @@ __global__ void __launch_bounds__(128) carry_tc_kernel(const CarryArgs a) {
         if (status == 0 && !tc::mbar_wait(&bars[0], par)) status = 3;
         tc::fence_after_sync();
         // ---- phase 2 operands: A0 = v rows, A1 = b rows (the phase-1 MMAs have finished reading A0/A1) ----
-        for (int c = 0; c < VP / 8; ++c) {
-            uint4 x = make_uint4(0, 0, 0, 0), y = x;
-            if (live && 8 * c < V) {
-                x = *reinterpret_cast<const uint4*>(gv + row * V + 8 * c);
-                y = *reinterpret_cast<const uint4*>(gb + row * V + 8 * c);
+        if (TMA) {
+            if (tid == 0 && status == 0) {
+                tc::mbar_expect_tx(&tbar, 2u * (unsigned)(VP / 64) * C_BOX);
+                for (int i = 0; i < VP / 64; ++i) {
+                    tc::tma_load_2d(A0 + i * C_BOX, &maps.v, h * V + 64 * i, (int)(bos + t0), &tbar);
+                    tc::tma_load_2d(A1 + i * C_BOX, &maps.b, h * V + 64 * i, (int)(bos + t0), &tbar);
+                }
             }
-            *reinterpret_cast<uint4*>(core_addr(A0, tid, c)) = x;
-            *reinterpret_cast<uint4*>(core_addr(A1, tid, c)) = y;
+        } else {
+            for (int c = 0; c < VP / 8; ++c) {
+                uint4 x = make_uint4(0, 0, 0, 0), y = x;
+                if (live && 8 * c < V) {
+                    x = *reinterpret_cast<const uint4*>(gv + row * V + 8 * c);
+                    y = *reinterpret_cast<const uint4*>(gb + row * V + 8 * c);
+                }
+                *reinterpret_cast<uint4*>(core_addr(A0, tid, c)) = x;
+                *reinterpret_cast<uint4*>(core_addr(A1, tid, c)) = y;
+            }
         }
         tc::fence_async_smem();
         tc::fence_before_sync();
         __syncthreads();
         if (tid == 0 && status == 0) {
             tc::fence_after_sync();
+            if (TMA) {
+                if (!tc::mbar_wait(&tbar, tpar)) status = 4;
+                tpar ^= 1;
+            }
+        }
+        if (tid == 0 && status == 0) {
             const unsigned a0 = tc::smem_u32(A0), a1 = tc::smem_u32(A1), brm = tc::smem_u32(B_RMt), bri = tc::smem_u32(B_RIt);
             for (int kk = 0; kk < VP / 16; ++kk) {
-                tc::mma(tmem + 256, tc::desc(a0 + kk * 256, C_LBO, C_SBO), tc::desc(brm + kk * 256, C_LBO, C_SBO), idesc_k, kk > 0);
-                tc::mma(tmem + 384, tc::desc(a1 + kk * 256, C_LBO, C_SBO), tc::desc(bri + kk * 256, C_LBO, C_SBO), idesc_k, kk > 0);
+                const unsigned so = (kk >> 2) * C_BOX + (kk & 3) * 32;
+                const unsigned long long dA0 = TMA ? tc::desc_sw128(a0 + so) : tc::desc(a0 + kk * 256, C_LBO, C_SBO);
+                const unsigned long long dA1 = TMA ? tc::desc_sw128(a1 + so) : tc::desc(a1 + kk * 256, C_LBO, C_SBO);
+                tc::mma(tmem + 256, dA0, tc::desc(brm + kk * 256, C_LBO, C_SBO), idesc_k, kk > 0);
+                tc::mma(tmem + 384, dA1, tc::desc(bri + kk * 256, C_LBO, C_SBO), idesc_k, kk > 0);
             }
             tc::commit(&bars[1]);
         }
@@ -353,11 +409,24 @@ int launch_carry_tc(const palimpsa_bwd_params* prm, const palimpsa_segments& sg,
     a.dk_x = reinterpret_cast<float*>(base + ws.dk_part) + (size_t)ws.tiles * rows * ws.KP;
     a.df_x = reinterpret_cast<float*>(base + ws.df_part) + (size_t)ws.tiles * rows;
     a.dip_x = reinterpret_cast<float*>(base + ws.dip_part) + (size_t)ws.tiles * rows;
-    const int smem = 6 * C_OPER;
-    if (cudaFuncSetAttribute(carry_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-        return PALIMPSA_E_LAUNCH;
+    const int smem = C_A0 + C_A1 + 4 * C_OPER + 1024;   // + slack to round the base up to 1024 bytes
     dim3 grid(p.num_seqs * p.H, sg.num_segments, 1);
-    carry_tc_kernel<<<grid, 128, smem, stream>>>(a);
+    // The k, v, b rows go in by TMA when a row of a head is whole 128-byte boxes (d_k, d_v multiples of 64) and the
+    // driver accepts the tensor maps (base 16-byte aligned, row pitch a multiple of 16 bytes: both hold here).
+    CarryMaps maps{};
+    const bool tma = p.K % 64 == 0 && p.V % 64 == 0 && p.total_tokens > 0 &&
+                     make_tensor_map_bf16_rows(&maps.k, p.k, (unsigned long long)p.total_tokens, (unsigned long long)p.H * p.K, CT) &&
+                     make_tensor_map_bf16_rows(&maps.v, p.v, (unsigned long long)p.total_tokens, (unsigned long long)p.H * p.V, CT) &&
+                     make_tensor_map_bf16_rows(&maps.b, p.b, (unsigned long long)p.total_tokens, (unsigned long long)p.H * p.V, CT);
+    if (tma) {
+        if (cudaFuncSetAttribute(carry_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return PALIMPSA_E_LAUNCH;
+        carry_tc_kernel<true><<<grid, 128, smem, stream>>>(a, maps);
+    } else {
+        if (cudaFuncSetAttribute(carry_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return PALIMPSA_E_LAUNCH;
+        carry_tc_kernel<false><<<grid, 128, smem, stream>>>(a, maps);
+    }
     return cudaGetLastError() == cudaSuccess ? PALIMPSA_OK : PALIMPSA_E_LAUNCH;
 }
 

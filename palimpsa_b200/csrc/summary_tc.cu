@@ -13,8 +13,10 @@
 //     two TMEM accumulators (S_M: columns 0..N-1, S_J: columns 128..128+N-1) and commits to an
 //     mbarrier per operand stage; two stages, so operand production overlaps the tensor pipe;
 //   * at the end every warp reads its 32 TMEM lanes back (tcgen05.ld) and writes fp32 rows.
-// No TMA: every operand is transformed in registers on its way (scaled, squared, transposed), so a
-// bulk copy into the MMA layout is not possible; global loads are plain 16-byte coalesced loads.
+// TMA feeds the one operand that is used exactly as it lies in global memory: k as the B operand of S_M.  Its
+// tile (64 tokens x d_k) is token-major, i.e. MN-major for the MMA, and arrives as cp.async.bulk.tensor boxes of
+// 64 tokens x 64 columns with the 128-byte swizzle (completion on an mbarrier per stage; d_k a multiple of 64).
+// The other three operands are transformed in registers on their way (scaled by a_t, squared, transposed).
 // Every wait is bounded; on a timeout the CTA records a status code, frees its TMEM and returns.
 #include "host.h"
 #include "tc_common.cuh"
@@ -26,7 +28,10 @@ constexpr int TC_ROWS = 128;                   // UMMA M
 constexpr int TC_SBO = (TCK / 8) * 128 + 16;   // bytes between 8-row groups of an operand (padded)
 constexpr int TC_LBO = 128;                    // bytes between the K-direction core matrices
 constexpr int TC_OPER = (TC_ROWS / 8) * TC_SBO;  // bytes of one operand tile
-constexpr int TC_STAGE = 4 * TC_OPER;          // A_M, A_J, B_M, B_J
+constexpr int TC_KBOX = TCK * 128;             // one TMA box of k: 64 tokens x 64 columns (128 bytes), swizzled
+constexpr int TC_TMA = 2 * TC_KBOX;            // d_k <= 128: two boxes
+constexpr int TC_STAGE = TC_TMA + 4 * TC_OPER; // [k by TMA] A_M, A_J, B_M (k by hand), B_J; a multiple of 1024 bytes
+static_assert(TC_STAGE % 1024 == 0, "stages must keep the 1024-byte alignment of the TMA boxes");
 
 __device__ int g_tc_status = 0;  // 0 ok; otherwise the first bounded wait that gave up (1: stage, 2: final)
 
@@ -37,9 +42,12 @@ struct TcArgs {
     int KP;
 };
 
-__global__ void __launch_bounds__(128) summary_tc_kernel(const TcArgs a) {
-    extern __shared__ __align__(128) unsigned char sm[];
+template <bool TMA>
+__global__ void __launch_bounds__(128) summary_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap kmap) {
+    extern __shared__ __align__(128) unsigned char sm_raw[];
+    unsigned char* sm = sm_raw + ((1024u - (tc::smem_u32(sm_raw) & 1023u)) & 1023u);   // TMA boxes: 1024-byte aligned
     __shared__ __align__(8) unsigned long long bars[2];
+    __shared__ __align__(8) unsigned long long tbars[2];   // completion of each stage's TMA load
     __shared__ unsigned tmem_base_s;
     __shared__ float a_s[TCK];
     __shared__ float lf_s[TCK];
@@ -57,7 +65,10 @@ __global__ void __launch_bounds__(128) summary_tc_kernel(const TcArgs a) {
     if (tid == 0) {
         tc::mbar_init(&bars[0]);
         tc::mbar_init(&bars[1]);
+        tc::mbar_init(&tbars[0]);
+        tc::mbar_init(&tbars[1]);
         tc::mbar_init_fence();
+        if (TMA) tc::tma_prefetch_map(&kmap);
     }
     if (w == 0) tc::tmem_alloc(&tmem_base_s, 256);
     tc::fence_before_sync();
@@ -96,6 +107,12 @@ __global__ void __launch_bounds__(128) summary_tc_kernel(const TcArgs a) {
         }
         __syncthreads();
         tc::fence_after_sync();
+        if (TMA && tid == 0 && status == 0) {   // k tile of the block straight into the stage (rows past the segment's
+            tc::mbar_expect_tx(&tbars[st], (unsigned)(KP / 64) * TC_KBOX);   // end meet zero rows of the A operands)
+            for (int x = 0; x < KP / 64; ++x)
+                tc::tma_load_2d(stage + x * TC_KBOX, &kmap, h * K + 64 * x, (int)(bos + t0), &tbars[st]);
+        }
+        unsigned char* opers = stage + TC_TMA;
         // ---- operands: thread (c, tp) handles 8 consecutive rows (chunk c) of a token pair ----
 #pragma unroll 1
         for (int it = 0; it < 4; ++it) {
@@ -104,21 +121,24 @@ __global__ void __launch_bounds__(128) summary_tc_kernel(const TcArgs a) {
             const float aa = a_s[ta], ab = a_s[tb];
             const long long rowa = ((long long)bos + t0 + ta) * p.H + h, rowb = rowa + p.H;
             const unsigned off = (unsigned)c * TC_SBO + (unsigned)(ta >> 3) * TC_LBO + (unsigned)(ta & 7) * 2;
-            auto emit = [&](const __nv_bfloat16* src, int dim, int oper, float wa, float wb, bool square, int oper2) {
+            auto emit = [&](const __nv_bfloat16* src, int dim, int oper, float wa, float wb, bool square, int oper2,
+                            bool first = true) {
                 uint4 xa = make_uint4(0, 0, 0, 0), xb = xa;
                 if (8 * c < dim) {
                     if (ta < nt) xa = *reinterpret_cast<const uint4*>(src + rowa * dim + 8 * c);
                     if (tb < nt) xb = *reinterpret_cast<const uint4*>(src + rowb * dim + 8 * c);
                 }
                 const unsigned ua[4] = {xa.x, xa.y, xa.z, xa.w}, ub[4] = {xb.x, xb.y, xb.z, xb.w};
-                unsigned char* dst = stage + oper * TC_OPER + off;
-                unsigned char* dst2 = stage + oper2 * TC_OPER + off;
+                unsigned char* dst = opers + oper * TC_OPER + off;
+                unsigned char* dst2 = opers + oper2 * TC_OPER + off;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float2 fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ua[j]));
                     const float2 fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ub[j]));
-                    *reinterpret_cast<unsigned*>(dst + (2 * j) * 16) = tc::pack_bf16(fa.x * wa, fb.x * wb);
-                    *reinterpret_cast<unsigned*>(dst + (2 * j + 1) * 16) = tc::pack_bf16(fa.y * wa, fb.y * wb);
+                    if (first) {
+                        *reinterpret_cast<unsigned*>(dst + (2 * j) * 16) = tc::pack_bf16(fa.x * wa, fb.x * wb);
+                        *reinterpret_cast<unsigned*>(dst + (2 * j + 1) * 16) = tc::pack_bf16(fa.y * wa, fb.y * wb);
+                    }
                     if (square) {
                         *reinterpret_cast<unsigned*>(dst2 + (2 * j) * 16) = tc::pack_bf16(fa.x * fa.x, fb.x * fb.x);
                         *reinterpret_cast<unsigned*>(dst2 + (2 * j + 1) * 16) = tc::pack_bf16(fa.y * fa.y, fb.y * fb.y);
@@ -127,20 +147,24 @@ __global__ void __launch_bounds__(128) summary_tc_kernel(const TcArgs a) {
             };
             emit(gv, V, 0, aa, ab, false, 0);   // A_M = a * v
             emit(gb, V, 1, aa, ab, false, 1);   // A_J = a * b
-            emit(gk, K, 2, 1.f, 1.f, true, 3);  // B_M = k, B_J = k*k
+            emit(gk, K, 2, 1.f, 1.f, true, 3, !TMA);  // B_J = k*k, and B_M = k unless TMA brings it
         }
         tc::fence_async_smem();
         tc::fence_before_sync();
         __syncthreads();
+        if (TMA && tid == 0 && status == 0 && !tc::mbar_wait(&tbars[st], use & 1)) status = 1;
         if (tid == 0 && status == 0) {
             tc::fence_after_sync();
-            const unsigned sbase = tc::smem_u32(stage);
+            const unsigned sbase = tc::smem_u32(opers), kbase = tc::smem_u32(stage);
 #pragma unroll
             for (int kk = 0; kk < TCK / 16; ++kk) {
                 const bool acc = i > 0 || kk > 0;
                 const unsigned ko = kk * 2 * TC_LBO;
-                tc::mma(tmem, tc::desc(sbase + 0 * TC_OPER + ko, TC_LBO, TC_SBO),
-                        tc::desc(sbase + 2 * TC_OPER + ko, TC_LBO, TC_SBO), idesc, acc);          // S_M += (a v)^T k
+                // k by TMA: MN-major boxes, a K = 16 step = 16 token rows = two 8-row groups of 1024 bytes
+                const unsigned long long dBM = TMA ? tc::desc_mn_sw128(kbase + kk * 2048, TC_KBOX)
+                                                   : tc::desc(sbase + 2 * TC_OPER + ko, TC_LBO, TC_SBO);
+                tc::mma(tmem, tc::desc(sbase + 0 * TC_OPER + ko, TC_LBO, TC_SBO), dBM,
+                        TMA ? (idesc | tc::IDESC_B_MN_MAJOR) : idesc, acc);                       // S_M += (a v)^T k
                 tc::mma(tmem + 128u, tc::desc(sbase + 1 * TC_OPER + ko, TC_LBO, TC_SBO),
                         tc::desc(sbase + 3 * TC_OPER + ko, TC_LBO, TC_SBO), idesc, acc);          // S_J += (a b)^T k^2
             }
@@ -206,11 +230,20 @@ int launch_summary_tc(const palimpsa_problem& p, const palimpsa_segments& sg, cu
     a.sum_J = sg.sum_J;
     a.decay = sg.decay;
     a.KP = palimpsa_padded_k(p.K);
-    const int smem = 2 * TC_STAGE;
-    if (cudaFuncSetAttribute(summary_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-        return PALIMPSA_E_LAUNCH;
+    const int smem = 2 * TC_STAGE + 1024;   // + slack to round the base up to 1024 bytes
     dim3 grid(p.num_seqs * p.H, sg.num_segments, 1);
-    summary_tc_kernel<<<grid, 128, smem, stream>>>(a);
+    CUtensorMap kmap{};
+    const bool tma = p.K % 64 == 0 && p.total_tokens > 0 &&
+                     make_tensor_map_bf16_rows(&kmap, p.k, (unsigned long long)p.total_tokens, (unsigned long long)p.H * p.K, TCK);
+    if (tma) {
+        if (cudaFuncSetAttribute(summary_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return PALIMPSA_E_LAUNCH;
+        summary_tc_kernel<true><<<grid, 128, smem, stream>>>(a, kmap);
+    } else {
+        if (cudaFuncSetAttribute(summary_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return PALIMPSA_E_LAUNCH;
+        summary_tc_kernel<false><<<grid, 128, smem, stream>>>(a, kmap);
+    }
     return cudaGetLastError() == cudaSuccess ? PALIMPSA_OK : PALIMPSA_E_LAUNCH;
 }
 
