@@ -127,6 +127,22 @@ __device__ __forceinline__ void st_dup4(float4* dst, int i, float4 x) {
 }
 
 
+// How the threads of a CTA split the 16-byte chunks of a [tokens][chunks] tile among themselves: thread ->
+// (first token, chunk), then every `step` tokens.  Computed once per kernel, so that the per-block copy loops
+// carry no integer division.  `step` = 0: the thread count is not a multiple of the chunk count (generic loop).
+struct ChunkSplit {
+    int t0, c, step;
+};
+__device__ __forceinline__ ChunkSplit chunk_split(int chunks, int nthr, int tid) {
+    ChunkSplit s{0, 0, 0};
+    if (chunks > 0 && chunks <= nthr && nthr % chunks == 0) {
+        s.t0 = tid / chunks;
+        s.c = tid - s.t0 * chunks;
+        s.step = nthr / chunks;
+    }
+    return s;
+}
+
 // Sum N per-lane values over the L lanes that differ from this one in the low log2(L) bits
 // (L = 2^s <= 32).  "Transposed" butterfly: each step exchanges half of the remaining values, so it
 // costs N-1 (+ a few) shuffles instead of N*log2(L).  On return x[i], i < max(1, N/L), holds the sum of

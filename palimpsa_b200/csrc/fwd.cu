@@ -87,28 +87,47 @@ __host__ __device__ inline FwdSmem fwd_smem_layout(int KP, int TV, int es, bool 
 
 // Issue the asynchronous copies of one block of nt tokens (aligned fast path only).
 __device__ __forceinline__ void fwd_issue(const FwdArgs& a, unsigned char* stage, const FwdSmem& L, int es, int KP,
-                                          int TV, long long tok0, int nt, int h, int v0, int tvw) {
+                                          int TV, long long tok0, int nt, int h, int v0, int tvw, const ChunkSplit& sq,
+                                          const ChunkSplit& sv) {
     const palimpsa_problem& p = a.p;
     const int nthr = blockDim.x, tid = threadIdx.x;
     const int cq = p.K * es / 16;
     const char* gq = reinterpret_cast<const char*>(p.q);
     const char* gk = reinterpret_cast<const char*>(p.k);
-    for (int i = tid; i < nt * cq; i += nthr) {
-        int t = i / cq, c = i - t * cq;
-        long long src = ((tok0 + t) * p.H + h) * (long long)p.K * es + c * 16;
-        int dst = t * KP * es + c * 16;
-        cp_async16(stage + L.rq + dst, gq + src);
-        cp_async16(stage + L.rk + dst, gk + src);
+    if (sq.step > 0) {
+        for (int t = sq.t0; t < nt; t += sq.step) {
+            long long src = ((tok0 + t) * p.H + h) * (long long)p.K * es + sq.c * 16;
+            int dst = t * KP * es + sq.c * 16;
+            cp_async16(stage + L.rq + dst, gq + src);
+            cp_async16(stage + L.rk + dst, gk + src);
+        }
+    } else {
+        for (int i = tid; i < nt * cq; i += nthr) {
+            int t = i / cq, c = i - t * cq;
+            long long src = ((tok0 + t) * p.H + h) * (long long)p.K * es + c * 16;
+            int dst = t * KP * es + c * 16;
+            cp_async16(stage + L.rq + dst, gq + src);
+            cp_async16(stage + L.rk + dst, gk + src);
+        }
     }
     const int cv = tvw * es / 16;
     const char* gv = reinterpret_cast<const char*>(p.v);
     const char* gb = reinterpret_cast<const char*>(p.b);
-    for (int i = tid; i < nt * cv; i += nthr) {
-        int t = i / cv, c = i - t * cv;
-        long long src = (((tok0 + t) * p.H + h) * (long long)p.V + v0) * es + c * 16;
-        int dst = t * TV * es + c * 16;
-        cp_async16(stage + L.rv + dst, gv + src);
-        cp_async16(stage + L.rb + dst, gb + src);
+    if (sv.step > 0) {
+        for (int t = sv.t0; t < nt; t += sv.step) {
+            long long src = (((tok0 + t) * p.H + h) * (long long)p.V + v0) * es + sv.c * 16;
+            int dst = t * TV * es + sv.c * 16;
+            cp_async16(stage + L.rv + dst, gv + src);
+            cp_async16(stage + L.rb + dst, gb + src);
+        }
+    } else {
+        for (int i = tid; i < nt * cv; i += nthr) {
+            int t = i / cv, c = i - t * cv;
+            long long src = (((tok0 + t) * p.H + h) * (long long)p.V + v0) * es + c * 16;
+            int dst = t * TV * es + c * 16;
+            cp_async16(stage + L.rv + dst, gv + src);
+            cp_async16(stage + L.rb + dst, gb + src);
+        }
     }
     for (int i = tid; i < nt; i += nthr) cp_async4(stage + L.rgt + i * 4, p.gt + (tok0 + i) * p.H + h);
 }
@@ -186,12 +205,25 @@ __device__ __forceinline__ void fwd_group(float2 (&M)[RV][RK / 4][2], float2 (&I
         const float4 fcv = fc[t];
         const float2 ff = make_float2(fcv.x, fcv.y), cc = make_float2(fcv.z, fcv.w);
         float2 vr[RV], br[RV], acc[RV], accv[RV];
+        if constexpr (RV % 2 == 0) {  // two adjacent duplicated pairs come in as one 16-byte load (row0 and TV are even)
 #pragma unroll
-        for (int r = 0; r < RV; ++r) {
-            vr[r] = vs2[t * TV + r];
-            br[r] = bs2[t * TV + r];
-            acc[r] = accv[r] = make_float2(0.f, 0.f);
+            for (int r = 0; r < RV; r += 2) {
+                const float4 v4 = *reinterpret_cast<const float4*>(vs2 + t * TV + r);
+                const float4 b4 = *reinterpret_cast<const float4*>(bs2 + t * TV + r);
+                vr[r] = make_float2(v4.x, v4.y);
+                vr[r + 1] = make_float2(v4.z, v4.w);
+                br[r] = make_float2(b4.x, b4.y);
+                br[r + 1] = make_float2(b4.z, b4.w);
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < RV; ++r) {
+                vr[r] = vs2[t * TV + r];
+                br[r] = bs2[t * TV + r];
+            }
         }
+#pragma unroll
+        for (int r = 0; r < RV; ++r) acc[r] = accv[r] = make_float2(0.f, 0.f);
 #pragma unroll
         for (int j = 0; j < J4; ++j) {
             const int idx = t * (KP / 4) + j * KG + kg;
@@ -325,9 +357,10 @@ __global__ void __launch_bounds__(32 * W) fwd_kernel(const FwdArgs a) {
     float* yvs = reinterpret_cast<float*>(sm + L.yvs);
     unsigned char* raw = sm + L.raw;
 
+    const ChunkSplit sq = chunk_split(K * es / 16, NTHR, tid), sv = chunk_split(tvw * es / 16, NTHR, tid);
     if (a.aligned && nblk > blk0) {
         fwd_issue(a, raw + (blk0 & 1) * L.raw_stage, L, es, KP, TV, (long long)bos + blk0 * TB, min(TB, s1 - blk0 * TB),
-                  h, v0, tvw);
+                  h, v0, tvw, sq, sv);
         cp_async_commit();
     }
 
@@ -339,7 +372,7 @@ __global__ void __launch_bounds__(32 * W) fwd_kernel(const FwdArgs a) {
         if (a.aligned) {
             if (blk + 1 < nblk) {
                 fwd_issue(a, raw + ((blk + 1) & 1) * L.raw_stage, L, es, KP, TV, tok0 + TB, min(TB, s1 - t0 - TB), h,
-                          v0, tvw);
+                          v0, tvw, sq, sv);
                 cp_async_commit();
                 cp_async_wait<1>();
             } else {
