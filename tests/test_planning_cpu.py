@@ -53,3 +53,14 @@ def test_missing_library_is_a_loud_error(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "libpalimpsa_b200.so"))
     with pytest.raises(_lib.PalimpsaLibraryError, match="no CPU or PyTorch fallback"):
         _lib.lib()
+
+
+def test_forward_tile_rows_from_the_library():
+    """Pure host function of the C ABI: rows of one forward CTA per head shape (what plan_segments counts CTAs with)."""
+    from palimpsa_b200 import _lib
+    lib = _lib.lib()
+    assert lib.palimpsa_fwd_tile_rows(128, 128) == 16
+    assert lib.palimpsa_fwd_tile_rows(64, 64) == 32
+    assert lib.palimpsa_fwd_tile_rows(64, 8) == 16         # short d_v: one warp instead of two, half the tile
+    assert lib.palimpsa_fwd_tile_rows(300, 64) == 0        # d_k above the supported maximum
+    assert lib.palimpsa_last_error_string(_lib.E_SYMBOL).startswith(b"the library's own scratch array")
