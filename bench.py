@@ -263,7 +263,7 @@ def dram_traffic(kernel, source, token_heads):
             cells = [c.strip().strip("`") for c in line.strip().strip("|").split("|")]
             if len(cells) >= 5 and cells[0] == kernel and cells[1] == sha:
                 try:
-                    return float(cells[2]) * token_heads / float(cells[3]), f"ncu capture of {cells[4]}, scaled by token-heads"
+                    return float(cells[2]) * token_heads / float(cells[3]), f"ncu capture of {cells[4]}; scaled by the units one launch processes"
                 except ValueError:
                     continue
     return None, f"no ncu capture of this kernel version ({source} sha256 {sha}) on record"
