@@ -580,9 +580,9 @@ def varlen_workload(dev, steps, warmup):
     return {"workload": f"C3 packed batch: {len(lens)} documents, {T} tokens, lengths {min(lens)}..{max(lens)}, H={H} "
                         f"d_k={K} d_v={V} bf16, states reset at document boundaries",
             "ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3), "steps": steps, "gpu_launches": 4 * (steps + max(3, warmup)),
-            "limited_by": "the longest documents: one CTA column walks a document serially, so the tail of the step "
-                          "runs with few CTAs (cutting the packed axis into segments was measured and does not pay "
-                          "on this mix)"}
+            "limited_by": "the longest documents: one CTA column walks a document serially; the kernels start the "
+                          "documents longest first (seq_order), which keeps the tail of the launch short; cutting the "
+                          "packed axis into segments was measured and does not pay on this mix"}
 
 
 def c5_workload(dev, rank, world, steps):

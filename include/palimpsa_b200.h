@@ -37,7 +37,7 @@
 extern "C" {
 #endif
 
-#define PALIMPSA_ABI_VERSION 7
+#define PALIMPSA_ABI_VERSION 8
 
 /* io dtype of q, k, v, b, o, o_var, do, do_var, dq, dk, dv, db */
 #define PALIMPSA_F32 0
@@ -82,6 +82,14 @@ typedef struct palimpsa_problem {
     const int32_t *chunk_offsets; /* [N] device: first checkpoint slot of each sequence =
                                      exclusive cumsum of ceil(len/16); NULL => n*ceil(T/16)     */
     const float *init_mu, *init_I; /* [N,H,V,K] or both NULL (=> mu=0, I=Ip)                     */
+    const int32_t *seq_order;     /* [N] device, or NULL: a permutation of 0..N-1 giving the order in
+                                     which the forward and backward main kernels hand sequences to
+                                     their CTAs (grid column i works on sequence seq_order[i]).  A
+                                     scheduling hint only -- results do not depend on it; packed
+                                     batches pass their sequences longest first, so that the long
+                                     documents do not end up as the tail of the launch.  The reference
+                                     has no counterpart (its programs take sequences in order,
+                                     chunk_palimpsa_forgetting_scalar.py:119-126).                */
 } palimpsa_problem;
 
 /* Forward.  Replaces chunk_palimpsa_fwd_kernel (chunk_palimpsa_forgetting_scalar.py:66-218) and

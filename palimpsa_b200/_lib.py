@@ -7,7 +7,7 @@ import os
 PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libpalimpsa_b200.so")
 
-ABI_VERSION = 7
+ABI_VERSION = 8
 F32, BF16, F16 = 0, 1, 2
 FLAG_UNCERTAINTY = 1
 FLAG_EXPLICIT_INIT = 2
@@ -25,7 +25,7 @@ class Problem(C.Structure):
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("b", C.c_void_p),
         ("gt", C.c_void_p), ("g", C.c_void_p), ("Ip", C.c_void_p),
         ("cu_seqlens", C.c_void_p), ("chunk_offsets", C.c_void_p),
-        ("init_mu", C.c_void_p), ("init_I", C.c_void_p),
+        ("init_mu", C.c_void_p), ("init_I", C.c_void_p), ("seq_order", C.c_void_p),
     ]
 
 

@@ -305,7 +305,8 @@ __global__ void __launch_bounds__(32 * W) bwd_kernel(const BwdArgs a) {
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int kg = lane % KG, vg = lane / KG, wv = w * VG + vg;
     const int row0 = wv * RV;
-    const int n = blockIdx.y / p.H, h = blockIdx.y - n * p.H;
+    const int ny = blockIdx.y / p.H, h = blockIdx.y - ny * p.H;
+    const int n = p.seq_order ? p.seq_order[ny] : ny;  // blocks start in grid order: a packed batch lists its longest sequences first
     const int tile = blockIdx.x;
     const int v0 = tile * TV;
     const int tvw = min(TV, p.V - v0);

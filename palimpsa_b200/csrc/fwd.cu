@@ -282,7 +282,8 @@ __global__ void __launch_bounds__(32 * W) fwd_kernel(const FwdArgs a) {
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int kg = lane % KG, vg = lane / KG;
     const int row0 = (w * VG + vg) * RV;
-    const int n = blockIdx.y / p.H, h = blockIdx.y - n * p.H;
+    const int ny = blockIdx.y / p.H, h = blockIdx.y - ny * p.H;
+    const int n = p.seq_order ? p.seq_order[ny] : ny;  // blocks start in grid order: a packed batch lists its longest sequences first
     const int v0 = blockIdx.x * TV;
     const int tvw = min(TV, p.V - v0);
     const int es = dtype_size(p.io_dtype);

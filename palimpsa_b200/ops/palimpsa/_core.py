@@ -26,7 +26,7 @@ def _ptr(t: Optional[Tensor]):
     return None if t is None or t.numel() == 0 else t.data_ptr()
 
 
-def _problem(q, k, v, b, gt, g, Ip, cu_seqlens, chunk_offsets, init_mu, init_I, scale, flags) -> L.Problem:
+def _problem(q, k, v, b, gt, g, Ip, cu_seqlens, chunk_offsets, init_mu, init_I, scale, flags, seq_order=None) -> L.Problem:
     B, T, H, K = q.shape
     V = v.shape[-1]
     p = L.Problem()
@@ -42,6 +42,7 @@ def _problem(q, k, v, b, gt, g, Ip, cu_seqlens, chunk_offsets, init_mu, init_I, 
     p.cu_seqlens = _ptr(cu_seqlens)
     p.chunk_offsets = _ptr(chunk_offsets)
     p.init_mu, p.init_I = _ptr(init_mu), _ptr(init_I)
+    p.seq_order = _ptr(seq_order)
     return p
 
 
@@ -66,6 +67,13 @@ def padded_k(K: int) -> int:
 
 def _ckpt_slots(total_tokens: int, num_seqs: int) -> int:
     return (total_tokens + L.CKPT_INTERVAL - 1) // L.CKPT_INTERVAL + num_seqs
+
+
+def _longest_first(cu_seqlens: Tensor) -> Tensor:
+    """Sequences of a packed batch by decreasing length (device-side, no host sync): the order in which the
+    main kernels start them, so that the longest documents are not the tail of the launch."""
+    lens = cu_seqlens[1:] - cu_seqlens[:-1]
+    return torch.argsort(lens, descending=True, stable=True).to(torch.int32)
 
 
 def _chunk_offsets(cu_seqlens: Tensor) -> Tensor:
@@ -150,6 +158,7 @@ def fwd_op(q: Tensor, k: Tensor, v: Tensor, b: Tensor, gt: Tensor, g: Tensor, Ip
         else:
             fmu = fI = None
         coff = _chunk_offsets(cu_seqlens) if cu_seqlens is not None else None
+        order = _longest_first(cu_seqlens) if cu_seqlens is not None and N > 1 else None
         if save_ckpt:
             slots = _ckpt_slots(B * T, N)
             ckM = torch.empty(slots, H, V, padded_k(K), dtype=torch.float32, device=dev)
@@ -159,7 +168,7 @@ def fwd_op(q: Tensor, k: Tensor, v: Tensor, b: Tensor, gt: Tensor, g: Tensor, Ip
         prm = L.FwdParams()
         prm.struct_size = C.sizeof(L.FwdParams)
         prm.p = _problem(q, k, v, b, gt, g, Ip, cu_seqlens, coff, init_mu, init_I, scale,
-                         L.FLAG_UNCERTAINTY if uncertainty else 0)
+                         L.FLAG_UNCERTAINTY if uncertainty else 0, order)
         prm.o, prm.o_var = _ptr(o), _ptr(o_var)
         prm.final_mu, prm.final_I = _ptr(fmu), _ptr(fI)
         prm.ckpt_M, prm.ckpt_I = _ptr(ckM), _ptr(ckI)
@@ -219,7 +228,8 @@ def bwd_op(do: Tensor, do_var: Optional[Tensor], q: Tensor, k: Tensor, v: Tensor
         flags = (L.FLAG_UNCERTAINTY if do_var is not None else 0) | (L.FLAG_EXPLICIT_INIT if explicit_init else 0)
         prm = L.BwdParams()
         prm.struct_size = C.sizeof(L.BwdParams)
-        prm.p = _problem(q, k, v, b, gt, g, Ip, cu_seqlens, chunk_offsets, None, None, scale, flags)
+        order = _longest_first(cu_seqlens) if cu_seqlens is not None and cu_seqlens.numel() > 2 else None
+        prm.p = _problem(q, k, v, b, gt, g, Ip, cu_seqlens, chunk_offsets, None, None, scale, flags, order)
         need = lib.palimpsa_bwd_workspace_bytes(C.byref(prm.p))
         ws = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
         prm.d_o, prm.d_o_var = _ptr(do), _ptr(do_var)
