@@ -26,6 +26,9 @@ def _worker(rank, world, port, q_out, cases):
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
         import datetime
         import torch.distributed as dist
+        # the float64 oracle runs on the host in every rank at once: keep the ranks' thread pools from
+        # oversubscribing the cores (tiny tensors: spinning OpenMP teams slow each other down by orders of magnitude)
+        torch.set_num_threads(max(1, (os.cpu_count() or 2) // (2 * world)))
         torch.cuda.set_device(rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120),
                                 device_id=torch.device("cuda", rank))
