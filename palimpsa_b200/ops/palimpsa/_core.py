@@ -286,6 +286,10 @@ def _setup_context(ctx, inputs, output):
     ctx.has_ckpt = save_ckpt
     ctx.varlen = cu_seqlens is not None
     ctx.save_for_backward(q, k, v, b, gt, g, Ip, cu_seqlens, coff, ckM, ckI, decay)
+    # Only `o` (and `o_var`) ever receive a gradient.  Without this, autograd hands the backward a ZERO tensor for
+    # every other float output -- including the two checkpoint buffers, i.e. 1.6 GB of fills per step at the
+    # benchmark's size.
+    ctx.set_materialize_grads(False)
 
 
 def _backward(ctx, do, do_var, dfmu, dfI, _dckM, _dckI, _dcoff, _ddecay):

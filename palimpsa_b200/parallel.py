@@ -223,6 +223,7 @@ class _CpChunkPalimpsa(torch.autograd.Function):
             chain_down(rank, world, group, loc.combine, loc.state_like())
             o, o_var, fmu, fI, ckM, ckI = loc.forward(save_ckpt=need_grad)
         ctx.loc, ctx.group, ctx.reduce = loc, group, reduce_param_grads
+        ctx.set_materialize_grads(False)                 # no zero tensors for outputs that received no gradient
         ctx.rank, ctx.world = rank, world
         if need_grad:
             # the inputs go through save_for_backward as well, so that an in-place change between forward and
