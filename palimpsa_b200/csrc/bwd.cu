@@ -752,7 +752,6 @@ __global__ void __launch_bounds__(256) bwd_finish_rows(const palimpsa_problem p,
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
     const int h = (int)(row % p.H);
-    const int KP2 = KP / 2;
     // per-token scalars: lane t fetches tile t's partial (tiles beyond 32 go round), summed by a fixed butterfly
     float df = 0.f, dip = 0.f;
     for (int t = lane; t < tiles_k; t += 32) {
@@ -760,36 +759,41 @@ __global__ void __launch_bounds__(256) bwd_finish_rows(const palimpsa_problem p,
         dip += dip_part[(size_t)t * rows + row];
     }
     const float gtv = p.gt[row], gh = p.g[h];
-    for (int pi = lane; pi < KP2; pi += 32) {
-        float2 sq = make_float2(0.f, 0.f), sk = sq;
-        const float2* pq = reinterpret_cast<const float2*>(dq_part) + (size_t)row * KP2 + pi;
-        const float2* pk = reinterpret_cast<const float2*>(dk_part) + (size_t)row * KP2 + pi;
-        const size_t step = (size_t)rows * KP2;
-#pragma unroll 4
+    // a lane owns four consecutive columns: one 16-byte load per tile partial, all tiles' loads independent
+    const int KP4 = KP / 4;
+    for (int c4 = lane; c4 < KP4; c4 += 32) {
+        float4 sq = make_float4(0.f, 0.f, 0.f, 0.f), sk = sq;
+        const float4* pq = reinterpret_cast<const float4*>(dq_part) + (size_t)row * KP4 + c4;
+        const float4* pk = reinterpret_cast<const float4*>(dk_part) + (size_t)row * KP4 + c4;
+        const size_t step = (size_t)rows * KP4;
+#pragma unroll 6
         for (int t = 0; t < tiles; ++t) {
-            const float2 x = pq[t * step], y = pk[t * step];
-            sq.x += x.x, sq.y += x.y;
-            sk.x += y.x, sk.y += y.y;
+            const float4 x = pq[t * step], y = pk[t * step];
+            sq.x += x.x, sq.y += x.y, sq.z += x.z, sq.w += x.w;
+            sk.x += y.x, sk.y += y.y, sk.z += y.z, sk.w += y.w;
         }
         if (tiles_k > tiles) {  // dk has one slot more than dq: the carried-gradient terms
-            const float2 y = pk[tiles * step];
-            sk.x += y.x, sk.y += y.y;
+            const float4 y = pk[tiles * step];
+            sk.x += y.x, sk.y += y.y, sk.z += y.z, sk.w += y.w;
         }
-        const int kc = 2 * pi;
-        if (pairs_ok) {
+        const int kc = 4 * c4;
+        if (pairs_ok) {          // K even, dq/dk 8-byte aligned: paired stores
             if (kc < p.K) {
-                st2(dq, row * p.K + kc, sq, p.io_dtype);
-                st2(dk, row * p.K + kc, sk, p.io_dtype);
+                st2(dq, row * p.K + kc, make_float2(sq.x, sq.y), p.io_dtype);
+                st2(dk, row * p.K + kc, make_float2(sk.x, sk.y), p.io_dtype);
+            }
+            if (kc + 2 < p.K) {
+                st2(dq, row * p.K + kc + 2, make_float2(sq.z, sq.w), p.io_dtype);
+                st2(dk, row * p.K + kc + 2, make_float2(sk.z, sk.w), p.io_dtype);
             }
         } else {
-            if (kc < p.K) {
-                st1(dq, row * p.K + kc, sq.x, p.io_dtype);
-                st1(dk, row * p.K + kc, sk.x, p.io_dtype);
-            }
-            if (kc + 1 < p.K) {
-                st1(dq, row * p.K + kc + 1, sq.y, p.io_dtype);
-                st1(dk, row * p.K + kc + 1, sk.y, p.io_dtype);
-            }
+            const float q4[4] = {sq.x, sq.y, sq.z, sq.w}, k4[4] = {sk.x, sk.y, sk.z, sk.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (kc + i < p.K) {
+                    st1(dq, row * p.K + kc + i, q4[i], p.io_dtype);
+                    st1(dk, row * p.K + kc + i, k4[i], p.io_dtype);
+                }
         }
     }
 #pragma unroll
