@@ -9,7 +9,9 @@ Runs, on cuda:0, from the unmodified working copy under ``oracle/_ref/``:
 1. ``palimpsa.layers.palimpsa.Palimpsa`` (palimpsa/layers/palimpsa.py:33-348) in training mode under bf16
    autocast: forward (the layer's chunk call, :309) and backward; output, input gradient and a few parameter
    gradients are saved.
-2. the same layer in eval mode with an FLA ``Cache``: a 100-token prefill (chunk mode, final states into the
+   The same for ``palimpsa.layers.meta_mamba2.MetaMamba2`` (palimpsa/layers/meta_mamba2.py:35-376), which calls
+   the ops with raw (unnormalised) q/k, ``scale=1.0`` and d_k = 32, d_v = 128 (:333).
+2. the Palimpsa layer in eval mode with an FLA ``Cache``: a 100-token prefill (chunk mode, final states into the
    cache) followed by three single-token steps (the layer's fused-recurrent call with cached states, :317).
 3. ``train_nano.py`` itself (train_nano.py:1-185), executed with ``runpy`` from the copy's folder with
    ``--max_iters N``; its printed losses and per-50-iteration times are parsed from its output.
@@ -64,6 +66,25 @@ def main():
               "dt_bias", "b_scale", "D", "g_proj.weight"):
         p = dict(layer.named_parameters())[n]
         res["train_grad_" + n] = p.grad.float().cpu()
+
+    # ---- 1b. the MetaMamba2 layer: raw q/k, scale = 1, d_k = 32 / d_v = 128 --------------------------------------
+    from palimpsa.layers import meta_mamba2 as mm2_mod
+    res["mm2_chunk_op_module"] = mm2_mod.chunk_palimpsa.__module__
+    torch.manual_seed(2)
+    mm2 = mm2_mod.MetaMamba2(num_heads=4, head_dim=128, hidden_size=256, state_size=32, expand=2, layer_idx=0,
+                             init_diagnosis=False).to(dev)
+    x2 = torch.randn(2, 160, 256, generator=gen).to(dev).requires_grad_(True)
+    w2 = torch.randn(2, 160, 256, generator=gen).to(dev)
+    mm2.train()
+    with torch.amp.autocast(device_type="cuda", dtype=torch.bfloat16):
+        y2, _, _ = mm2(x2)
+    (y2.float() * w2).sum().backward()
+    res["mm2_out"] = y2.detach().float().cpu()
+    res["mm2_dx"] = x2.grad.float().cpu()
+    for n, prm in mm2.named_parameters():
+        if prm.grad is not None:
+            res["mm2_grad_" + n] = prm.grad.float().cpu()
+    del mm2
 
     # ---- 2. eval: prefill with cache, then single-token decode steps -----------------------------------------
     layer.eval()

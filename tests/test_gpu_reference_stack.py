@@ -7,6 +7,7 @@ reference untouched (Triton ops), the other calls ``palimpsa_b200.install_as_pal
 
 * the ``Palimpsa`` layer in training mode (chunk call, palimpsa/layers/palimpsa.py:309): output, input
   gradient, parameter gradients;
+* the ``MetaMamba2`` layer in training mode (raw q/k, ``scale=1.0``, palimpsa/layers/meta_mamba2.py:333);
 * prefill + cached single-token steps in eval mode (fused-recurrent call with cached states, :317-331);
 * ``train_nano.py`` (train_nano.py:163-185) for 100 iterations from the same seed: the evaluation losses at
   step 0 and the training losses it prints at iterations 0, 50 and 100.
@@ -52,6 +53,17 @@ def test_reference_layer_training_step(arms):
     errs = {n: orc.rel_err(a[n], b[n]) for n in a if n.startswith("train_")}
     print("\nreference layer, training mode, CUDA ops vs Triton ops:", {n: f"{e:.1e}" for n, e in errs.items()})
     assert all(torch.isfinite(a[n]).all() for n in errs)
+    assert max(errs.values()) <= 3e-2, errs
+
+
+def test_reference_meta_mamba2_layer_training_step(arms):
+    """The reference's second caller: raw q/k, ``scale=1.0``, d_k = 32, d_v = 128 (palimpsa/layers/meta_mamba2.py:333)."""
+    a, b = arms["cuda"], arms["triton"]
+    assert a["mm2_chunk_op_module"].startswith("palimpsa_b200.")
+    names = [n for n in a if n.startswith("mm2_") and torch.is_tensor(a[n])]
+    errs = {n: orc.rel_err(a[n], b[n]) for n in names}
+    print("\nreference MetaMamba2 layer, training mode, CUDA ops vs Triton ops:", {n: f"{e:.1e}" for n, e in errs.items()})
+    assert len(names) >= 6 and all(torch.isfinite(a[n]).all() for n in names)
     assert max(errs.values()) <= 3e-2, errs
 
 
