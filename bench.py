@@ -788,6 +788,7 @@ def run_ours(args, rank, world, local_rank):
                     "ms_per_step": ms_e2e / e2e_steps, "api": "palimpsa_b200.host_pipeline.HostPipeline.run",
                     "slice_widths": slice_widths, "copy_only_ms": ms_copy,
                     "copy_only_gbs_per_rank_per_direction": h2d / (ms_copy * 1e-3) / 1e9,
+                    "copy_only_frac_of_e2e": ms_copy / (ms_e2e / e2e_steps),
                     "resident_ms": ms / args.steps},
             "gpu_launches": launches, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu_line,
             "gpu_baseline": gpu_line, "workloads": workloads}
