@@ -186,7 +186,8 @@ int palimpsa_chunk_bwd_segments(const palimpsa_bwd_params *params, const palimps
 /* Adds the terms that are linear in the end-state gradients segs->carry_M/carry_I to a backward that
  * ran with mode 2: dv, db are updated in place, the dk / dgt / dg / dIp terms go to a partial slot of
  * the workspace that mode 3 sums.  Four [tokens x d]*[d x d] products per segment on the tensor cores
- * (tcgen05, TMEM accumulators).  bf16 io without uncertainty output, d_v <= 128, padded d_k in
+ * (tcgen05, TMEM accumulators; the k, v, b token rows arrive by TMA when d_k and d_v are multiples of 64).
+ * bf16 io without uncertainty output, d_v <= 128, padded d_k in
  * {32,64,96,128}: palimpsa_carry_apply_supported() tells; otherwise use modes 1 and 0. */
 int palimpsa_carry_apply_supported(const palimpsa_problem *p);
 int palimpsa_carry_apply(const palimpsa_bwd_params *params, const palimpsa_segments *segs, void *cuda_stream);
