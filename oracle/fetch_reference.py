@@ -10,6 +10,7 @@ beside this repository):
     palimpsa/                    ops (Triton chunk / fused-recurrent kernels, ``palimpsa_ref``), layers, models
     train_nano.py                the character-level trainer (train_nano.py:1-185)
     data/shakespeare_char/       its corpus and tokeniser script
+    config/palimpsa_170M.json    the 170M model's shape (for a packed variable-length model step)
 
 and then runs the copied ``data/shakespeare_char/prepare.py`` once so that ``train.bin`` / ``val.bin`` /
 ``meta.pkl`` exist beside it (the script finds ``input.txt`` and downloads nothing).
@@ -32,7 +33,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
 TREES = ("palimpsa",)
-FILES = ("train_nano.py", "data/shakespeare_char/input.txt", "data/shakespeare_char/prepare.py")
+FILES = ("train_nano.py", "data/shakespeare_char/input.txt", "data/shakespeare_char/prepare.py",
+         "config/palimpsa_170M.json")
 
 
 def default_source() -> str:

@@ -16,6 +16,11 @@ Runs, on cuda:0, from the unmodified working copy under ``oracle/_ref/``:
 3. ``train_nano.py`` itself (train_nano.py:1-185), executed with ``runpy`` from the copy's folder with
    ``--max_iters N``; its printed losses and per-50-iteration times are parsed from its output.
 
+4. a packed variable-length TRAINING STEP of the reference's ``PalimpsaForCausalLM`` in the 170M model's shape
+   (config/palimpsa_170M.json: 16 heads of d_k = d_v = 48; 4 of its 19 layers), the way its Flame recipe feeds it
+   (README.md:135-158: one packed row, ``cu_seqlens`` through the model's kwargs to every layer,
+   palimpsa/models/palimpsa/modeling_palimpsa.py:255-262): loss, a few gradients and the step time.
+
 Writes everything into ``--out`` (torch.save).  The parent test compares the two arms' files.
 """
 import argparse
@@ -126,6 +131,55 @@ def main():
                                for m in re.finditer(r"iter (\d+): loss [0-9.]+, time ([0-9.]+)ms", text)}
         res["nano_eval"] = {int(m.group(1)): (float(m.group(2)), float(m.group(3)))
                             for m in re.finditer(r"step (\d+): train loss ([0-9.]+), val loss ([0-9.]+)", text)}
+    # ---- 4. packed variable-length training step of the 170M-shaped model ------------------------------------
+    try:
+        import json
+        from palimpsa.models.palimpsa.configuration_palimpsa import PalimpsaConfig
+        from palimpsa.models.palimpsa.modeling_palimpsa import PalimpsaForCausalLM
+        with open(os.path.join(REF, "config", "palimpsa_170M.json")) as f:
+            cfg = {k: v for k, v in json.load(f).items() if k not in ("architectures", "auto_map", "model_type")}
+        # 4 layers; untied embeddings (the installed transformers release rejects the reference's list-typed
+        # _tied_weights_keys when the config ties them -- a packaging matter, not part of the path under test)
+        cfg.update(num_hidden_layers=4, use_cache=False, tie_word_embeddings=False)
+        torch.manual_seed(3)
+        model = PalimpsaForCausalLM(PalimpsaConfig(**cfg)).to(dev)
+        model.train()
+        T = 16384
+        g2 = torch.Generator().manual_seed(4)
+        lens, tot = [], 0
+        while tot < T:                                       # documents of 128 .. 4096 tokens, as the recipe packs them
+            n = min(int(torch.randint(128, 4097, (1,), generator=g2).item()), T - tot)
+            lens.append(n)
+            tot += n
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+        ids = torch.randint(0, cfg["vocab_size"], (1, T), generator=g2).to(dev)
+
+        def step():
+            model.zero_grad(set_to_none=True)
+            with torch.amp.autocast(device_type="cuda", dtype=torch.bfloat16):
+                out = model(ids, labels=ids, cu_seqlens=cu)
+            out.loss.backward()
+            return out.loss
+
+        loss = step()
+        torch.cuda.synchronize()
+        res["varlen_loss"] = float(loss)
+        params = dict(model.named_parameters())
+        for n in ("model.embeddings.weight", "model.layers.0.attn.q_proj.weight", "model.layers.0.attn.A_log",
+                  "model.layers.0.attn.b_proj.weight", "model.layers.3.attn.dt_bias", "model.layers.3.attn.v_proj.weight"):
+            if n in params and params[n].grad is not None:
+                res["varlen_grad_" + n] = params[n].grad.float().cpu()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        res["varlen_step_ms"] = e0.elapsed_time(e1) / 3
+        res["varlen_documents"] = len(lens)
+    except Exception as e:                                    # noqa: BLE001  (reported by the parent test)
+        import traceback
+        res["varlen_error"] = traceback.format_exc()[-1500:]
     torch.save(res, a.out)
     print(f"{a.ops} arm done: chunk op from {res['chunk_op_module']}")
 

@@ -9,6 +9,8 @@ reference untouched (Triton ops), the other calls ``palimpsa_b200.install_as_pal
   gradient, parameter gradients;
 * the ``MetaMamba2`` layer in training mode (raw q/k, ``scale=1.0``, palimpsa/layers/meta_mamba2.py:333);
 * prefill + cached single-token steps in eval mode (fused-recurrent call with cached states, :317-331);
+* a packed variable-length training step of the 170M-shaped ``PalimpsaForCausalLM`` (``cu_seqlens`` through the
+  model's kwargs, as the Flame recipe README.md:135-158 does): loss, gradients, step time;
 * ``train_nano.py`` (train_nano.py:163-185) for 100 iterations from the same seed: the evaluation losses at
   step 0 and the training losses it prints at iterations 0, 50 and 100.
 
@@ -92,3 +94,19 @@ def test_train_nano_loss_curve(arms):
         x, y = a["nano_iter_loss"][i], b["nano_iter_loss"][i]
         assert abs(x - y) <= 5e-2 * y, (i, x, y)
     assert a["nano_iter_loss"][last] < 0.8 * a["nano_iter_loss"][0]
+
+
+def test_packed_variable_length_model_step(arms):
+    """The 170M-shaped ``PalimpsaForCausalLM`` (4 of its layers) on one packed row with ``cu_seqlens``, forward +
+    backward, the way the reference's Flame recipe drives it: same loss and gradients on both op sets."""
+    a, b = arms["cuda"], arms["triton"]
+    if "varlen_error" in b:
+        pytest.skip("the reference stack itself could not run the packed step here: " + b["varlen_error"][-300:])
+    assert "varlen_error" not in a, a.get("varlen_error")
+    names = [n for n in a if n.startswith("varlen_grad_")]
+    errs = {n[12:]: orc.rel_err(a[n], b[n]) for n in names}
+    print(f"\npacked 170M-shaped model step ({a['varlen_documents']} documents, 16 384 tokens): loss {a['varlen_loss']:.4f} "
+          f"(CUDA ops) vs {b['varlen_loss']:.4f} (Triton ops); step {a['varlen_step_ms']:.1f} ms vs {b['varlen_step_ms']:.1f} ms;",
+          {n: f"{e:.1e}" for n, e in errs.items()})
+    assert abs(a["varlen_loss"] - b["varlen_loss"]) <= 2e-3 * abs(b["varlen_loss"])
+    assert len(names) >= 4 and max(errs.values()) <= 5e-2, errs
