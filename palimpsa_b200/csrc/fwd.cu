@@ -273,10 +273,16 @@ __device__ __forceinline__ void fwd_group(float2 (&M)[RV][RK / 4][2], float2 (&I
     }
 }
 
+// The d_k = 128 tiling (16 state elements per thread, 16 lanes per row) reduces 8 tokens' outputs in one butterfly
+// and is held to 128 registers (4 CTAs of 4 warps per SM): 1.57 -> 1.49 ms on the 170M shape.  The other tilings
+// keep batches of 4 and the compiler's own register count (8 there costs them spills).
+template <int RK, int KG, int RV, bool UNC>
+constexpr bool fwd_small_tile = RK * RV <= 16 && KG == 16 && !UNC;
+
 template <int RK, int KG, int RV, int W, bool UNC, bool SUM>
-__global__ void __launch_bounds__(32 * W) fwd_kernel(const FwdArgs a) {
+__global__ void __launch_bounds__(32 * W, fwd_small_tile<RK, KG, RV, UNC> ? 4 : 1) fwd_kernel(const FwdArgs a) {
     constexpr int KP = RK * KG, VG = 32 / KG, J4 = RK / 4, TV = W * VG * RV, NTHR = 32 * W;
-    constexpr int GF = 4;  // tokens whose outputs are reduced together
+    constexpr int GF = fwd_small_tile<RK, KG, RV, UNC> ? 8 : 4;  // tokens whose outputs are reduced together
     extern __shared__ __align__(16) unsigned char sm[];
     const palimpsa_problem& p = a.p;
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
