@@ -589,6 +589,50 @@ def varlen_workload(dev, steps, warmup):
                           "packed axis into segments was measured and does not pay on this mix"}
 
 
+MODEL_SHAPES = (  # head shapes of the reference's shipped model configurations: (name, B, T, H, d_k, d_v)
+    ("palimpsa_170M (config/palimpsa_170M.json: 16 heads of 48)", 8, 4096, 16, 48, 48),
+    ("meta_mamba2_170M (config/meta_mamba2_170M.json: state 48, head 96)", 8, 4096, 16, 48, 96),
+    ("not_palimpsa_760M (config/not_palimpsa_760M.json: d_k 96, d_v 192)", 8, 4096, 16, 96, 192),
+    ("mqar (zoology/mqar_figure/configs.py: 8 heads, d_k 16, d_v 32)", 64, 512, 8, 16, 32),
+)
+
+
+def model_shapes_workload(dev, steps, with_reference):
+    """Chunk forward + backward (bf16, 32 768 tokens per step) at the head shapes the reference's shipped model
+    configurations imply, beside the reference's Triton ops (chunk_size 16, as its layers pass) when its working copy
+    is present.  ``tflops`` counts the operator's 40 * d_k * d_v flop per token-head."""
+    chunk = None
+    if with_reference:
+        try:
+            chunk = _load_reference_op("chunk_palimpsa_forgetting_scalar.py", "chunk_palimpsa")
+        except Exception:                                 # noqa: BLE001
+            chunk = None
+    rows, launches = [], 0
+    for name, B, T, H, K, V in MODEL_SHAPES:
+        from palimpsa_b200.ops.palimpsa._core import plan_segments
+        _, d = make_inputs(B, T, H, K, V, torch.bfloat16, dev, seed=0, on_device=True)
+        ms = time_region(lambda: fwd_bwd(d), steps, 3, 1, dev) / steps
+        G = plan_segments(B, T, H, K, V, dev, backward=True)
+        launches += (8 if G > 1 else 4) * (steps + 3)
+        row = {"shape": name, "B": B, "T": T, "H": H, "d_k": K, "d_v": V, "segments": G, "ms_per_step": ms,
+               "tokens_per_s": B * T / (ms * 1e-3), "tflops": 40.0 * K * V * B * T * H / (ms * 1e-3) / 1e12}
+        if chunk is not None:
+            try:
+                def step():
+                    leaves = [d[n].detach().requires_grad_(True) for n in NAMES]
+                    chunk(*leaves, chunk_size=16).backward(d["do"])
+                rms = time_region(step, 2, 2, 1, dev) / 2
+                row.update(reference_triton_ms_per_step=rms, speedup=rms / ms)
+            except Exception as e:                        # noqa: BLE001
+                row["reference_triton"] = f"unavailable: {type(e).__name__}: {str(e)[:120]}"
+                torch.cuda.synchronize(dev)
+        rows.append(row)
+        del d
+        torch.cuda.empty_cache()
+    return {"workload": "chunk fwd+bwd at the head shapes of the reference's shipped configurations, bf16",
+            "shapes": rows, "gpu_launches": launches}
+
+
 def c5_workload(dev, rank, world, steps):
     """C5: one 131 072-token sequence, H=12, d_k=d_v=128, bf16 fwd+bwd.  N=1: the single-GPU op with the planner's
     segments.  N>=2: ``cp_chunk_palimpsa`` over the N ranks (each rank holds T/N contiguous tokens; boundary states
@@ -599,7 +643,7 @@ def c5_workload(dev, rank, world, steps):
     single_ms = None
     if rank == 0:
         _, d = make_inputs(B, T, H, K, V, torch.bfloat16, dev, seed=0, on_device=True)
-        G = plan_segments(B, T, H, K, V, dev)
+        G = plan_segments(B, T, H, K, V, dev, backward=True)
         n1 = max(2, min(steps, 5))
         single_ms = time_region(lambda: fwd_bwd(d), n1, 2, 1, dev) / n1
         out["single_gpu"] = {"ms_per_step": single_ms, "tokens_per_s": T / (single_ms * 1e-3), "segments": G,
@@ -653,7 +697,7 @@ def c2_strong_workload(dev, rank, world, steps, warmup, single_ms):
     else:
         step = lambda: None
     ms = time_region(step, steps, max(3, warmup), world, dev) / steps
-    G = plan_segments(max(hi - lo, 1), T, H, K, V, dev)
+    G = plan_segments(max(hi - lo, 1), T, H, K, V, dev, backward=True)
     out = {"workload": f"C2 global batch B={B} T={T} H={H} sharded by (sequence, head) over {world} GPUs, no collective",
            "n_gpus": world, "units_per_gpu": (hi - lo) * H, "segments_per_sequence": G, "ms_per_step": ms,
            "tokens_per_s": B * T / (ms * 1e-3)}
@@ -738,7 +782,7 @@ def run_ours(args, rank, world, local_rank):
     d2h = sum(x.numel() * x.element_size() for x in out_host.values())
     ms_copy = time_host_region(lambda: copies_only(pipe, host, dev), e2e_steps, 2, world, dev) / e2e_steps
     from palimpsa_b200.ops.palimpsa._core import plan_segments
-    per_e2e_step = sum(8 if plan_segments(hi - lo, T, H, K, V, dev) > 1 else 4 for lo, hi in pipe.bounds)
+    per_e2e_step = sum(8 if plan_segments(hi - lo, T, H, K, V, dev, backward=True) > 1 else 4 for lo, hi in pipe.bounds)
     slice_widths = [hi - lo for lo, hi in pipe.bounds]
     del pipe, out_host
 
@@ -767,7 +811,9 @@ def run_ours(args, rank, world, local_rank):
         if rank == 0 and world == 1:
             workloads["decode"] = decode_workload(dev, args.decode_steps)
             workloads["varlen"] = varlen_workload(dev, max(3, min(args.steps, 10)), 3)
-            launches += workloads["decode"]["gpu_launches"] + workloads["varlen"]["gpu_launches"]
+            workloads["model_shapes"] = model_shapes_workload(dev, max(3, min(args.steps, 5)), True)
+            launches += (workloads["decode"]["gpu_launches"] + workloads["varlen"]["gpu_launches"] +
+                         workloads["model_shapes"]["gpu_launches"])
         elif rank == 0:
             workloads["decode"] = workloads["varlen"] = {"skipped": "measured at n_gpus = 1 (independent per "
                                                                     "sequence: ranks would run disjoint shards)"}

@@ -37,7 +37,7 @@
 extern "C" {
 #endif
 
-#define PALIMPSA_ABI_VERSION 8
+#define PALIMPSA_ABI_VERSION 9
 
 /* io dtype of q, k, v, b, o, o_var, do, do_var, dq, dk, dv, db */
 #define PALIMPSA_F32 0
@@ -188,7 +188,7 @@ int palimpsa_chunk_bwd_segments(const palimpsa_bwd_params *params, const palimps
  * the workspace that mode 3 sums.  Four [tokens x d]*[d x d] products per segment on the tensor cores
  * (tcgen05, TMEM accumulators; the k, v, b token rows arrive by TMA when d_k and d_v are multiples of 64).
  * bf16 io without uncertainty output, d_v <= 128, padded d_k in
- * {32,64,96,128}: palimpsa_carry_apply_supported() tells; otherwise use modes 1 and 0. */
+ * {32,48,64,96,128}: palimpsa_carry_apply_supported() tells; otherwise use modes 1 and 0. */
 int palimpsa_carry_apply_supported(const palimpsa_problem *p);
 int palimpsa_carry_apply(const palimpsa_bwd_params *params, const palimpsa_segments *segs, void *cuda_stream);
 
@@ -206,6 +206,13 @@ int palimpsa_padded_k(int K);
  * to decide whether a problem fills the GPU or should be cut into segments.  No counterpart in the reference,
  * whose grid is fixed at (V/16) x N x H programs (chunk_palimpsa_forgetting_scalar.py:478). */
 int palimpsa_fwd_tile_rows(int K, int V);
+
+/* The same for the backward kernel, whose tile also depends on the element type (PALIMPSA_F32 / _BF16 / _F16) and on
+ * whether the uncertainty output takes part (shared-memory budget): a backward launch has ceil(V / rows) x num_seqs x
+ * H CTAs of up to 12 warps, usually one resident per SM, so hosts that plan a training step count waves with it.
+ * 0 if the shape is not supported.  No counterpart in the reference (grid (V/16) x N x H,
+ * chunk_palimpsa_forgetting_scalar.py:558). */
+int palimpsa_bwd_tile_rows(int K, int V, int io_dtype, int uncertainty);
 
 /* Upper bound on checkpoint slots for a problem: ceil(total_tokens/16) + num_seqs (varlen needs
  * no host synchronisation to size its buffers). */

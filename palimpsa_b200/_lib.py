@@ -7,7 +7,7 @@ import os
 PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libpalimpsa_b200.so")
 
-ABI_VERSION = 8
+ABI_VERSION = 9
 F32, BF16, F16 = 0, 1, 2
 FLAG_UNCERTAINTY = 1
 FLAG_EXPLICIT_INIT = 2
@@ -96,6 +96,7 @@ SYMBOLS = {
     "palimpsa_last_error_string": (C.c_char_p, [C.c_int]),
     "palimpsa_padded_k": (C.c_int, [C.c_int]),
     "palimpsa_fwd_tile_rows": (C.c_int, [C.c_int, C.c_int]),
+    "palimpsa_bwd_tile_rows": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "palimpsa_ckpt_slots": (C.c_longlong, [C.POINTER(Problem)]),
     "palimpsa_segment_summary": (C.c_int, [C.POINTER(Problem), C.POINTER(Segments), C.c_void_p]),
     "palimpsa_tensor_core_status": (C.c_int, []),

@@ -104,6 +104,17 @@ int palimpsa_padded_k(int K) {
     return 0;
 }
 
+int palimpsa_bwd_tile_rows(int K, int V, int io_dtype, int uncertainty) {
+    if (K <= 0 || V <= 0 || K > PALIMPSA_MAX_K) return 0;
+    if (io_dtype != PALIMPSA_F32 && io_dtype != PALIMPSA_BF16 && io_dtype != PALIMPSA_F16) return 0;
+    palimpsa_problem p{};
+    p.K = K;
+    p.V = V;
+    p.io_dtype = io_dtype;
+    p.flags = uncertainty ? PALIMPSA_FLAG_UNCERTAINTY : 0;
+    return bwd_tile_rows(p);
+}
+
 int palimpsa_fwd_tile_rows(int K, int V) {
     if (K <= 0 || V <= 0 || K > PALIMPSA_MAX_K) return 0;
     return fwd_tile_rows(K, V);
@@ -145,7 +156,10 @@ int palimpsa_segment_summary(const palimpsa_problem* p, const palimpsa_segments*
     rc = check_segments(*p, sg);
     if (rc) return rc;
     if (!sg->sum_M || !sg->sum_J || !sg->decay) return PALIMPSA_E_NULL;
-    if (summary_tc_supported(*p)) return launch_summary_tc(*p, *sg, static_cast<cudaStream_t>(cuda_stream));
+    // The tensor-core kernel costs the same per token whatever the head size (128-row tiles); below about
+    // 8192 state elements per head the element-wise summary pass is the faster one (measured on 48x48 .. 128x128).
+    if (summary_tc_supported(*p) && (long long)palimpsa_padded_k(p->K) * p->V >= 8192)
+        return launch_summary_tc(*p, *sg, static_cast<cudaStream_t>(cuda_stream));
     palimpsa_fwd_params prm{};
     prm.struct_size = sizeof(prm);
     prm.p = *p;

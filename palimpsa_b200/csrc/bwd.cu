@@ -873,6 +873,8 @@ static BwdConfig bwd_config(const palimpsa_problem& p) {
         const int pad11 = (p.V + 21) / 22 * 22, pad12 = (p.V + 23) / 24 * 24;
         W = pad11 < pad12 ? 11 : 12;
     }
+    // d_k = 48 (8 rows per warp): 6 warps = 48 rows where that pads d_v with fewer idle rows than 64 (d_v = 48, 96, 144)
+    if (KP == 48 && rpw == 8 && W == 8 && (p.V + 47) / 48 * 48 < (p.V + 63) / 64 * 64) W = 6;
     for (;;) {
         c.W = W;
         c.TV = W * rpw;
@@ -882,7 +884,7 @@ static BwdConfig bwd_config(const palimpsa_problem& p) {
             c.kbuf = 1;
             c.smem = bwd_smem_layout(KP, c.TV, c.s.RV * c.s.RK, 32 * W, W * VG, es, unc, 1).total;
         }
-        if (c.smem <= 227 * 1024 || W == 4 || rpw == 1 || W >= 11) break;
+        if (c.smem <= 227 * 1024 || W == 4 || rpw == 1 || W >= 11) break;  // 6 and 8 fall back to 4
         W = 4;
     }
     return c;
@@ -948,6 +950,8 @@ static int launch_bwd_t(const BwdArgs& args, int tiles, int num_seg, bool carry_
     BwdArgs a = args;
     a.kbuf = cfg.kbuf;
     if (cfg.W == 8) return launch_bwd_w<RK, KG, RV, 8>(a, tiles, num_seg, carry_only, stream);
+    if constexpr (RK == 6 && KG == 8 && RV == 2)
+        if (cfg.W == 6) return launch_bwd_w<RK, KG, RV, 6>(a, tiles, num_seg, carry_only, stream);
     if constexpr (RK == 4 && KG == 32 && RV == 2) {
         if (cfg.W == 12) return launch_bwd_w<RK, KG, RV, 12>(a, tiles, num_seg, carry_only, stream);
         if (cfg.W == 11) return launch_bwd_w<RK, KG, RV, 11>(a, tiles, num_seg, carry_only, stream);

@@ -327,6 +327,7 @@ __global__ void __launch_bounds__(128) carry_tc_kernel(const CarryArgs a, const 
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const int col = c0 + 8 * q;
+                        if (col >= KP) continue;   // padded d_k = 48: columns past the accumulator hold nothing
                         uint4 kx = make_uint4(0, 0, 0, 0);
                         if (col < K) kx = *reinterpret_cast<const uint4*>(gk + row * K + col);
                         const unsigned* pk = reinterpret_cast<const unsigned*>(&kx);
@@ -385,7 +386,7 @@ bool carry_tc_supported(const palimpsa_problem& p) {
     const int KP = palimpsa_padded_k(p.K);
     auto al = [](const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15) == 0; };
     return p.io_dtype == PALIMPSA_BF16 && !(p.flags & PALIMPSA_FLAG_UNCERTAINTY) && p.V <= 128 && p.V % 8 == 0 &&
-           p.K % 8 == 0 && KP >= 32 && KP <= 128 && KP % 32 == 0 && al(p.k) && al(p.v) && al(p.b);
+           p.K % 8 == 0 && KP >= 32 && KP <= 128 && KP % 16 == 0 && al(p.k) && al(p.v) && al(p.b);
 }
 
 int launch_carry_tc(const palimpsa_bwd_params* prm, const palimpsa_segments& sg, cudaStream_t stream) {

@@ -532,6 +532,9 @@ static int launch_fwd_w(const FwdArgs& a, int num_seg, bool summary, cudaStream_
 template <int RK, int KG, int RV, int WMAX>
 static int fwd_warps(int V) {
     constexpr int RPW = (32 / KG) * RV;
+    // d_k = 48 (16 rows per warp): 3 warps = 48 rows where that pads d_v with fewer idle rows than 64 (d_v = 48, 96, 144)
+    if constexpr (RK == 12 && KG == 4 && RV == 2 && WMAX == 4)
+        if (V > 32 && (V + 47) / 48 * 48 < (V + 63) / 64 * 64) return 3;
     if constexpr (WMAX >= 4 && (RPW * (WMAX / 4)) % 8 == 0)
         if (V <= RPW * (WMAX / 4)) return WMAX / 4;
     if constexpr (WMAX >= 2 && (RPW * (WMAX / 2)) % 8 == 0)
@@ -542,6 +545,8 @@ static int fwd_warps(int V) {
 template <int RK, int KG, int RV, int WMAX>
 static int launch_fwd_t(const FwdArgs& a, int num_seg, bool summary, cudaStream_t stream) {
     const int W = fwd_warps<RK, KG, RV, WMAX>(a.p.V);
+    if constexpr (RK == 12 && KG == 4 && RV == 2 && WMAX == 4)
+        if (W == 3) return launch_fwd_w<RK, KG, RV, 3>(a, num_seg, summary, stream);
     if constexpr (WMAX >= 4)
         if (W == WMAX / 4) return launch_fwd_w<RK, KG, RV, WMAX / 4>(a, num_seg, summary, stream);
     if constexpr (WMAX >= 2)

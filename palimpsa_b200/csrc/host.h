@@ -21,7 +21,7 @@ int launch_decode(const palimpsa_fwd_params* prm, cudaStream_t stream);
 int launch_bwd(const palimpsa_bwd_params* prm, const palimpsa_segments* segs, bool carry_only, cudaStream_t stream,
                int stages);
 
-// Segment summaries on the tensor cores (summary_tc.cu): bf16 inputs, d_v <= 128, padded d_k in {32,64,96,128}.
+// Segment summaries on the tensor cores (summary_tc.cu): bf16 inputs, d_v <= 128, padded d_k in {32,48,64,96,128}.
 bool summary_tc_supported(const palimpsa_problem& p);
 int launch_summary_tc(const palimpsa_problem& p, const palimpsa_segments& segs, cudaStream_t stream);
 int summary_tc_status();

@@ -17,7 +17,7 @@ from ... import _lib as L
 _DT = {torch.float32: L.F32, torch.bfloat16: L.BF16, torch.float16: L.F16}
 
 # Segmented backward: take the tensor-core route for the carried-gradient terms wherever the library supports
-# the problem (bf16, d_v <= 128, padded d_k in {32,64,96,128}).  Tests set this to False to exercise the
+# the problem (bf16, d_v <= 128, padded d_k in {32,48,64,96,128}).  Tests set this to False to exercise the
 # two-pass CUDA-core route on the same problems.
 carry_on_tensor_cores = True
 
@@ -99,16 +99,33 @@ def sm_count(device=None) -> int:
 
 
 @torch.compiler.assume_constant_result        # ints in, int out: evaluated once when a caller is traced by torch.compile
-def plan_segments(N: int, T: int, H: int, K: int, V: int, device=None) -> int:
+def plan_segments(N: int, T: int, H: int, K: int, V: int, device=None, backward: bool = False,
+                  io_dtype: int = L.BF16, uncertainty: bool = False) -> int:
     """How many segments to cut every sequence into on one GPU.  Segments cost an extra summary pass
-    (and the carried-gradient terms in backward), so they are only used when the (sequence, head,
-    row-tile) grid of the forward kernel alone would leave SMs idle, e.g. one very long sequence or a narrow
-    batch slice.  The row-tile height comes from the library, the SM count from the device."""
-    rows = L.lib().palimpsa_fwd_tile_rows(int(K), int(V))
+    (and the carried-gradient terms in backward: about a fifth of a step), so they are only used when the grid of
+    (sequence, head, row-tile) CTAs would leave SMs idle, e.g. one very long sequence or a narrow batch slice.
+
+    Forward only: the forward grid has fewer CTAs than the device has SMs.  With a backward to follow
+    (``backward=True``) the backward kernel decides, since it is 3/4 of the step and keeps one CTA of up to 12 warps
+    per SM: segments when its grid fills less than 80 % of the waves it occupies (72 CTAs on 148 SMs, or 192 CTAs =
+    1.3 waves; not 128 CTAs = 0.86 of a wave, nor 288 = 1.95 waves).  Tile heights come from the library, the SM
+    count from the device."""
+    if T < 2048:
+        return 1
+    lib = L.lib()
+    sms = sm_count(device)
+    rows = lib.palimpsa_fwd_tile_rows(int(K), int(V))
     if rows <= 0:
         raise ValueError(f"d_k = {K} is above the supported maximum of 256")
-    ctas = N * H * ((V + rows - 1) // rows)
-    if ctas >= sm_count(device) or T < 2048:
+    if backward:
+        brow = lib.palimpsa_bwd_tile_rows(int(K), int(V), int(io_dtype), int(bool(uncertainty)))
+        if brow <= 0:
+            raise ValueError(f"no backward tiling for d_k = {K}, d_v = {V}")
+        ctas = N * H * ((V + brow - 1) // brow)
+        waves = (ctas + sms - 1) // sms
+        if ctas >= 0.8 * waves * sms:
+            return 1
+    elif N * H * ((V + rows - 1) // rows) >= sms:
         return 1
     # The boundary passes' total work does not depend on the number of segments, and their own grids
     # (one CTA per sequence x head x segment) want many of them: cut down to 256 tokens, at most 32 pieces
@@ -352,7 +369,8 @@ def run(q, k, v, b, gt, g, Ip, initial_mu_state, initial_I_state, scale, output_
     gt, g, Ip = [x.float().contiguous() for x in (gt, g, Ip)]
     save_ckpt = torch.is_grad_enabled() and any(x.requires_grad for x in (q, k, v, b, gt, g, Ip))
     if num_segments is None:
-        num_segments = 1 if cu_seqlens is not None else plan_segments(N, T, H, K, V, q.device)
+        num_segments = 1 if cu_seqlens is not None else plan_segments(
+            N, T, H, K, V, q.device, backward=bool(save_ckpt), io_dtype=_DT[io], uncertainty=bool(output_uncertainty))
     o, o_var, fmu, fI, _, _, _, _ = fwd_op(q, k, v, b, gt, g, Ip, initial_mu_state, initial_I_state, cu_seqlens,
                                            float(scale), bool(output_uncertainty), save_ckpt, bool(output_final_state),
                                            recurrent, int(num_segments))

@@ -285,7 +285,8 @@ def cp_chunk_palimpsa(q, k, v, b, gt, g, Ip, group=None, scale=None, output_fina
     gt, g, Ip = [x.float().contiguous() for x in (gt, g, Ip)]
     B, T, H, K = q.shape
     if num_segments is None:
-        num_segments = _core.plan_segments(B, T, H, K, v.shape[-1], q.device)
+        num_segments = _core.plan_segments(B, T, H, K, v.shape[-1], q.device, backward=torch.is_grad_enabled(),
+                                            io_dtype=_core._DT.get(q.dtype, L.BF16))
     if (initial_mu_state is None) != (initial_I_state is None):
         raise ValueError("pass both initial_mu_state and initial_I_state, or neither")
     if initial_mu_state is not None:

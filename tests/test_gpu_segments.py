@@ -100,7 +100,8 @@ def test_tensor_core_carry_terms_match_oracle_and_cuda_core_path(monkeypatch):
         assert orc.rel_err(tc_path[n], simt[n]) < 1e-2, n
 
 
-@pytest.mark.parametrize("K,V,T,G", [(64, 128, 300, 3), (128, 64, 260, 2), (32, 48, 130, 2)])
+@pytest.mark.parametrize("K,V,T,G", [(64, 128, 300, 3), (128, 64, 260, 2), (32, 48, 130, 2), (48, 48, 300, 3), (48, 96, 260, 2),
+                                     (96, 96, 200, 2)])
 def test_tensor_core_carry_other_shapes(K, V, T, G):
     inp = orc.make_inputs(K + V + T, B=1, T=T, H=2, K=K, V=V, dtype=torch.bfloat16)
     inp["gt"] = inp["gt"] * 0.05

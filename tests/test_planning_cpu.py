@@ -10,6 +10,15 @@ def test_plan_segments():
     assert plan_segments(1, 131072, 12, 128, 128) == 32    # long sequence: capped at 32 pieces
     assert plan_segments(1, 1024, 2, 64, 64) == 1          # short sequences never
     assert plan_segments(1, 2048, 1, 64, 64) == 8
+    # with a backward to follow, the backward grid decides (one CTA of up to 12 warps per SM, 148 SMs assumed here)
+    kw = dict(backward=True)
+    assert plan_segments(8, 4096, 6, 128, 128, **kw) == 1     # 288 CTAs of 22 rows = 1.95 waves
+    assert plan_segments(4, 4096, 6, 128, 128, **kw) == 1     # 144 CTAs = 0.97 of a wave
+    assert plan_segments(5, 4096, 6, 128, 128, **kw) == 16    # 180 CTAs = 1.2 waves: the second one mostly idle
+    assert plan_segments(2, 4096, 6, 128, 128, **kw) == 16    # 72 CTAs: half the SMs idle
+    assert plan_segments(8, 4096, 16, 48, 48, **kw) == 1      # the 170M model's heads: 128 CTAs = 0.86 of a wave
+    assert plan_segments(8, 4096, 12, 64, 64, **kw) == 16     # 192 CTAs = 1.3 waves
+    assert plan_segments(8, 1024, 12, 64, 64, **kw) == 1      # short sequences never
     for T, G in ((4096, 16), (333, 3), (17, 4), (1, 1)):
         L = segment_len(T, G)
         assert L % 16 == 0 and L * G >= T and L >= 16
@@ -63,4 +72,11 @@ def test_forward_tile_rows_from_the_library():
     assert lib.palimpsa_fwd_tile_rows(64, 64) == 32
     assert lib.palimpsa_fwd_tile_rows(64, 8) == 16         # short d_v: one warp instead of two, half the tile
     assert lib.palimpsa_fwd_tile_rows(300, 64) == 0        # d_k above the supported maximum
+    assert lib.palimpsa_fwd_tile_rows(48, 48) == 48        # three warps: no idle rows at the 170M model's heads
+    assert lib.palimpsa_bwd_tile_rows(128, 128, _lib.BF16, 0) == 22   # 11 warps x 2 rows: 6 tiles = 132 rows
+    assert lib.palimpsa_bwd_tile_rows(48, 48, _lib.BF16, 0) == 48     # 6 warps x 8 rows
+    assert lib.palimpsa_bwd_tile_rows(48, 96, _lib.BF16, 0) == 48
+    assert lib.palimpsa_bwd_tile_rows(64, 64, _lib.BF16, 0) == 32
+    assert lib.palimpsa_bwd_tile_rows(300, 64, _lib.BF16, 0) == 0
+    assert lib.palimpsa_bwd_tile_rows(64, 64, 99, 0) == 0             # unknown element type
     assert lib.palimpsa_last_error_string(_lib.E_SYMBOL).startswith(b"the library's own scratch array")
