@@ -22,8 +22,9 @@ def chunk_palimpsa(q, k, v, b, gt, g, Ip, initial_mu_state=None, initial_I_state
 
     ``num_segments`` (keyword-only, not in the reference): cut every sequence into that many segments
     that run side by side (boundary states from a summary pass and a scan); default: chosen from the
-    problem size, 1 unless the grid would leave most SMs idle (always 1 with ``cu_seqlens``, where an
-    explicit value cuts the packed token axis: segments past a sequence's end are empty).
+    problem size, 1 unless the grid would leave SMs idle.  With ``cu_seqlens`` the packed token axis is what is
+    cut (segments of ``T / num_segments`` tokens; those past a sequence's end are empty), and the default only does
+    so when there are too few documents to fill one wave of CTAs.
     """
     if scale is None:
         scale = q.shape[-1] ** -0.5

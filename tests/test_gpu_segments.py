@@ -65,6 +65,19 @@ def test_segments_in_a_packed_batch(dtype, G):
     compare(got, ref, TOL_FP32 if dtype == torch.float32 else TOL_BF16, what=f"packed + segments {dtype} G={G}")
 
 
+def test_packed_batch_with_few_documents_is_segmented_by_default():
+    """Three documents x two heads cannot fill the GPU: the planner cuts the packed axis (T / 256 = 10 segments of
+    ~256 tokens) without being asked, and the results still match the float64 oracle."""
+    from palimpsa_b200.ops.palimpsa._core import plan_segments
+    cu = [0, 1500, 1700, 2560]
+    assert plan_segments(3, 2560, 2, 64, 64, backward=True, packed=True) == 10
+    inp = orc.make_inputs(33, B=1, T=2560, H=2, K=64, V=64, dtype=torch.float32)
+    inp["gt"] = inp["gt"] * 0.1
+    got = _run(inp, None, cu=cu)
+    ref = run_oracle(inp, cu=cu)
+    compare(got, ref, TOL_FP32, what="packed batch, planner's segments")
+
+
 def test_segments_bf16_match_unsegmented():
     inp = orc.make_inputs(9, B=1, T=2048, H=2, K=128, V=128, dtype=torch.bfloat16)
     inp["gt"] = inp["gt"] * 0.05

@@ -19,6 +19,11 @@ def test_plan_segments():
     assert plan_segments(8, 4096, 16, 48, 48, **kw) == 1      # the 170M model's heads: 128 CTAs = 0.86 of a wave
     assert plan_segments(8, 4096, 12, 64, 64, **kw) == 16     # 192 CTAs = 1.3 waves
     assert plan_segments(8, 1024, 12, 64, 64, **kw) == 1      # short sequences never
+    # packed rows: only the document count is known; segments when the documents alone cannot fill one wave
+    assert plan_segments(7, 16384, 16, 48, 48, packed=True, **kw) == 32     # 112 CTAs: the longest document binds
+    assert plan_segments(14, 32768, 16, 48, 48, packed=True, **kw) == 1     # 224 CTAs, started longest first
+    assert plan_segments(14, 32768, 6, 128, 128, packed=True, **kw) == 1
+    assert plan_segments(3, 32768, 6, 128, 128, packed=True) == 32          # forward only: 144 forward CTAs
     for T, G in ((4096, 16), (333, 3), (17, 4), (1, 1)):
         L = segment_len(T, G)
         assert L % 16 == 0 and L * G >= T and L >= 16
