@@ -608,8 +608,8 @@ def model_shapes_workload(dev, steps, with_reference):
         except Exception:                                 # noqa: BLE001
             chunk = None
     rows, launches = [], 0
+    from palimpsa_b200.ops.palimpsa._core import plan_segments
     for name, B, T, H, K, V in MODEL_SHAPES:
-        from palimpsa_b200.ops.palimpsa._core import plan_segments
         _, d = make_inputs(B, T, H, K, V, torch.bfloat16, dev, seed=0, on_device=True)
         ms = time_region(lambda: fwd_bwd(d), steps, 3, 1, dev) / steps
         G = plan_segments(B, T, H, K, V, dev, backward=True)

@@ -141,7 +141,9 @@ typedef struct palimpsa_segments {
     float *rloc_M, *rloc_I;    /* backward: dL/d(start state of the segment), (M, I) form        */
 } palimpsa_segments;
 
-/* Fills sum_M, sum_J and decay for every segment (no reciprocal, no output: the cheap pass). */
+/* Fills sum_M, sum_J and decay for every segment (no reciprocal, no output: the cheap pass).  bf16 problems with
+ * d_v <= 128 and at least 8192 state elements per head (padded d_k x d_v) run as two GEMMs on the tensor cores
+ * (tcgen05, k by TMA when d_k is a multiple of 64); everything else element by element on the CUDA cores. */
 int palimpsa_segment_summary(const palimpsa_problem *p, const palimpsa_segments *segs, void *cuda_stream);
 
 /* Diagnostic: 0 unless a bounded wait inside a kernel gave up on this device since the last call of this

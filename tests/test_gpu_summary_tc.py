@@ -1,4 +1,5 @@
-"""Tensor-core (tcgen05/TMEM) segment summaries against the CUDA-core summaries and the float64 identity."""
+"""Segment summaries through the C ABI against the float64 identity: the tensor-core (tcgen05/TMEM) kernel, which the
+library picks for bf16 heads of at least 8192 state elements, and the element-wise kernel it picks below that."""
 import ctypes as C
 
 import pytest
@@ -27,8 +28,9 @@ def _summaries(inp, G, env_simt):
     return bufs, _core.segment_len(T, G)
 
 
-@pytest.mark.parametrize("K,V,T,G", [(128, 128, 500, 3), (64, 128, 200, 2), (128, 64, 130, 1), (32, 48, 70, 2)])
-def test_tensor_core_summary_matches_identity(K, V, T, G):
+@pytest.mark.parametrize("K,V,T,G", [(128, 128, 500, 3), (64, 128, 200, 2), (128, 64, 130, 1), (96, 96, 150, 2),   # tensor cores
+                                     (32, 48, 70, 2), (48, 48, 200, 3)])                                          # element-wise
+def test_segment_summary_matches_identity(K, V, T, G):
     from palimpsa_b200 import _lib as L
     inp = orc.make_inputs(K + T, B=2, T=T, H=2, K=K, V=V, dtype=torch.bfloat16)
     inp["gt"] = inp["gt"] * 0.1
