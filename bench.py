@@ -664,13 +664,24 @@ def c5_workload(dev, rank, world, steps):
         leaves = [loc[n].detach().requires_grad_(True) for n in NAMES]
         cp_chunk_palimpsa(*leaves).backward(loc["do"])
 
+    def step_nccl():
+        leaves = [loc[n].detach().requires_grad_(True) for n in NAMES]
+        cp_chunk_palimpsa(*leaves, transport="nccl").backward(loc["do"])
+
+    from palimpsa_b200.parallel import PeerLink
     n = max(3, min(steps, 10))
-    ms = time_region(step, n, 3, world, dev) / n
+    ms = time_region(step, n, 3, world, dev) / n                 # transport "auto": peer-mapped buffers where available
     hop = 2 * B * H * V * padded_k(K) * 4
+    peer = PeerLink.get(None, hop // 4, dev) is not None
+    ms_nccl = time_region(step_nccl, n, 3, world, dev) / n if peer else ms
     out.update(ms_per_step=ms, tokens_per_s=T / (ms * 1e-3), n_gpus=world, tokens_per_rank=hi - lo,
                bytes_per_hop=hop, hops_per_step=2 * (world - 1),
-               collective="torch.distributed send/recv (NCCL) of the boundary state, one message per hop, down in "
-                          "forward and up in backward; all-reduce of dg, dIp (2*H floats)",
+               transport="peer-mapped buffers: the boundary-scan kernel stores into the next rank's memory over "
+                         "NVLink, bounded wait / signal kernels order the hand-over" if peer else
+                         "torch.distributed send/recv (NCCL)",
+               ms_per_step_send_recv=ms_nccl,
+               collective="one 1.5 MB boundary state per hop, down in forward and up in backward; all-reduce of dg, "
+                          "dIp (2*H floats)",
                limited_by="the rank-to-rank chain is serial: 2*(N-1) hops of one small message plus one boundary-scan "
                           "kernel each; the heavy kernels run on all ranks side by side")
     if single_ms is not None:

@@ -37,7 +37,7 @@
 extern "C" {
 #endif
 
-#define PALIMPSA_ABI_VERSION 9
+#define PALIMPSA_ABI_VERSION 10
 
 /* io dtype of q, k, v, b, o, o_var, do, do_var, dq, dk, dv, db */
 #define PALIMPSA_F32 0
@@ -148,7 +148,7 @@ int palimpsa_segment_summary(const palimpsa_problem *p, const palimpsa_segments 
 
 /* Diagnostic: 0 unless a bounded wait inside a kernel gave up on this device since the last call of this
  * function; then the code of the wait (1, 2: tensor-core summary kernel; 3, 4: tensor-core carried-gradient
- * kernel; 5, 6: barriers of the backward main kernel).  Every in-kernel wait of this library is bounded: a
+ * kernel; 5, 6: barriers of the backward main kernel; 7: palimpsa_peer_wait).  Every in-kernel wait of this library is bounded: a
  * kernel that gives up records the code, releases what it holds and returns.  Its results are invalid, and it
  * marks them so that the failure cannot pass unnoticed: the summary kernel writes NaN into the segment's decay
  * (every later output becomes NaN), the other two write NaN into the decay-gradient partials (dgt of the
@@ -169,6 +169,22 @@ int palimpsa_cp_combine(const palimpsa_problem *p, const palimpsa_segments *segs
  * (out_M, out_I), if given, receive dL/d(start state of segment 0). */
 int palimpsa_cp_combine_bwd(const palimpsa_problem *p, const palimpsa_segments *segs, const float *in_M,
                             const float *in_I, float *out_M, float *out_I, void *cuda_stream);
+
+/* Hand-over of a boundary state between the GPUs of one node without a host round trip or a library call per hop.
+ * The exchange buffers of the ranks are mapped into each other's address space (CUDA peer / symmetric memory: the
+ * host arranges that); the producer hands palimpsa_cp_combine[_bwd] an out_M/out_J pointer INTO THE NEXT RANK'S
+ * buffer, then enqueues palimpsa_peer_signal(flag in the next rank's memory, n): a system-scope fence and a
+ * release store of the sequence number n, ordered after everything enqueued on the stream before it.  The consumer
+ * enqueues palimpsa_peer_wait(its own flag, n, ...) before the kernels that read the buffer: the stream is held
+ * until the flag has reached n (8-byte aligned unsigned 64-bit flags, sequence numbers only grow).  The wait
+ * is bounded: after timeout_ms of wall-clock time it records code 7 for palimpsa_tensor_core_status(), writes a NaN
+ * to *poison if given (the first element of the buffer it guards, so the failure shows in the results) and lets
+ * the stream go on.  Plain loads and stores over NVLink; no multimem, no bulk copies.  Nothing in the reference
+ * corresponds (torch.distributed send/recv of the same state is the other transport of
+ * palimpsa_b200.parallel.cp_chunk_palimpsa). */
+int palimpsa_peer_wait(const void *flag, unsigned long long value, unsigned int timeout_ms, float *poison,
+                       void *cuda_stream);
+int palimpsa_peer_signal(void *flag, unsigned long long value, void *cuda_stream);
 
 /* palimpsa_chunk_fwd with every segment started from segs->start_M/start_I. */
 int palimpsa_chunk_fwd_segments(const palimpsa_fwd_params *params, const palimpsa_segments *segs,

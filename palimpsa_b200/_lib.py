@@ -7,13 +7,13 @@ import os
 PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libpalimpsa_b200.so")
 
-ABI_VERSION = 9
+ABI_VERSION = 10
 F32, BF16, F16 = 0, 1, 2
 FLAG_UNCERTAINTY = 1
 FLAG_EXPLICIT_INIT = 2
 CKPT_INTERVAL = 16
 STATIC_SCRATCH_BYTES = 64 << 20
-E_LIMIT, E_SYMBOL = -9, -10
+E_NULL, E_ALIGN, E_LIMIT, E_SYMBOL = -1, -7, -9, -10
 
 
 class Problem(C.Structure):
@@ -97,6 +97,8 @@ SYMBOLS = {
     "palimpsa_padded_k": (C.c_int, [C.c_int]),
     "palimpsa_fwd_tile_rows": (C.c_int, [C.c_int, C.c_int]),
     "palimpsa_bwd_tile_rows": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int]),
+    "palimpsa_peer_wait": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint32, C.c_void_p, C.c_void_p]),
+    "palimpsa_peer_signal": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p]),
     "palimpsa_ckpt_slots": (C.c_longlong, [C.POINTER(Problem)]),
     "palimpsa_segment_summary": (C.c_int, [C.POINTER(Problem), C.POINTER(Segments), C.c_void_p]),
     "palimpsa_tensor_core_status": (C.c_int, []),

@@ -16,7 +16,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 ROOT = os.path.dirname(PKG)
 LIB = os.path.join(PKG, "libpalimpsa_b200.so")
-UNITS = ("abi", "fwd", "bwd", "decode", "segments", "summary_tc", "carry_tc", "layer")
+UNITS = ("abi", "fwd", "bwd", "decode", "segments", "summary_tc", "carry_tc", "layer", "peer")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--extended-lambda",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 

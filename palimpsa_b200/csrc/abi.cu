@@ -168,8 +168,20 @@ int palimpsa_segment_summary(const palimpsa_problem* p, const palimpsa_segments*
 
 int palimpsa_tensor_core_status(void) {
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-    const int a = summary_tc_status(), b = carry_tc_status(), c = bwd_wait_status();  // each clears what it read
-    return a ? a : (b ? b : c);
+    const int a = summary_tc_status(), b = carry_tc_status(), c = bwd_wait_status(), d = peer_status();  // each clears what it read
+    return a ? a : (b ? b : (c ? c : d));
+}
+
+int palimpsa_peer_wait(const void* flag, unsigned long long value, unsigned int timeout_ms, float* poison, void* cuda_stream) {
+    if (!flag) return PALIMPSA_E_NULL;
+    if ((reinterpret_cast<uintptr_t>(flag) & 7) != 0) return PALIMPSA_E_ALIGN;
+    return launch_peer_wait(flag, value, timeout_ms, poison, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int palimpsa_peer_signal(void* flag, unsigned long long value, void* cuda_stream) {
+    if (!flag) return PALIMPSA_E_NULL;
+    if ((reinterpret_cast<uintptr_t>(flag) & 7) != 0) return PALIMPSA_E_ALIGN;
+    return launch_peer_signal(flag, value, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int palimpsa_carry_apply_supported(const palimpsa_problem* p) { return p && carry_tc_supported(*p) ? 1 : 0; }

@@ -38,6 +38,11 @@ int launch_combine_fwd(const palimpsa_problem& p, const palimpsa_segments& segs,
 int launch_combine_bwd(const palimpsa_problem& p, const palimpsa_segments& segs, const float* in_M, const float* in_I,
                        float* out_M, float* out_I, cudaStream_t stream);
 
+// Stream-ordered flags in peer-mapped memory (peer.cu): a bounded wait until *flag >= value, and a release store.
+int launch_peer_wait(const void* flag, unsigned long long value, unsigned timeout_ms, float* poison, cudaStream_t stream);
+int launch_peer_signal(void* flag, unsigned long long value, cudaStream_t stream);
+int peer_status();   // 0, or 7 when a wait ran out
+
 // Backward whose scratch is the library's own fixed device array (bwd.cu).
 int launch_bwd_static(const palimpsa_bwd_params* prm, cudaStream_t stream);
 

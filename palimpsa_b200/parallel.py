@@ -17,6 +17,11 @@ come from the external trainer):
 The hop logic is written against a small backend interface so that the protocol can be exercised with
 CPU ranks (gloo) and a float64 stand-in for the kernels; the product backend below drives the CUDA
 library through its C ABI.
+
+Two transports for the hop.  ``"nccl"``: ``torch.distributed`` send / recv of the state.  ``"peer"`` (default on one
+node when the ranks' buffers can be mapped into each other's address space): the boundary-scan kernel stores its
+result straight into the next rank's buffer over NVLink and two one-thread kernels of the library order the
+hand-over on the stream (:class:`PeerLink`); no host round trip and no library call per hop.
 """
 from __future__ import annotations
 
@@ -83,6 +88,111 @@ def chain_up(rank: int, world: int, group, local: Callable[[Optional[torch.Tenso
         dist.send(out.contiguous(), dst=_peer(group, rank - 1), group=group)
 
 
+class PeerLink:
+    """Exchange buffers of the ranks of one node, mapped into each other's address space (torch symmetric memory:
+    CUDA virtual-memory handles exchanged through the process group's store).  Every rank owns::
+
+        [ready_down, ack_down, ready_up, ack_up : uint64, 64 bytes in all][inbox_down : n floats][inbox_up : n floats]
+
+    Direction 0 ("down") carries the boundary state from rank r to r+1, direction 1 ("up") the state gradient from
+    r+1 to r.  The producer's kernel writes into the consumer's inbox through the mapped pointer, then publishes the
+    sequence number of the call in the consumer's ``ready`` flag; the consumer, once its kernels have read the inbox,
+    publishes the same number in the producer's ``ack`` flag, and the producer waits for the previous number there
+    before it overwrites the inbox.  Sequence numbers only grow, so nothing is ever reset.  Every rank must make the
+    same sequence of calls (as with any collective).  All waits are the library's bounded ones."""
+
+    FLAG_FLOATS = 16                                        # 64 bytes of flags in front of the inboxes
+    _links = {}                                             # (group id, numel) -> PeerLink, or None if unavailable
+
+    def __init__(self, group, numel: int, device, timeout_ms: int = 20000):
+        import torch.distributed._symmetric_memory as symm
+        self.n, self.timeout_ms = int(numel), int(timeout_ms)
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.buf = symm.empty(self.FLAG_FLOATS + 2 * self.n, dtype=torch.float32, device=device)
+        self.buf.zero_()
+        self.hdl = symm.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
+        self.ptrs = [int(x) for x in self.hdl.buffer_ptrs]
+        if len(self.ptrs) != self.world or self.ptrs[self.rank] != self.buf.data_ptr():
+            raise RuntimeError("symmetric memory returned an unexpected set of buffers")
+        self.epoch = [0, 0]
+        torch.cuda.synchronize(device)
+
+    def inbox(self, d: int) -> torch.Tensor:
+        lo = self.FLAG_FLOATS + d * self.n
+        return self.buf[lo:lo + self.n]
+
+    def inbox_ptr(self, rank: int, d: int) -> int:
+        return self.ptrs[rank] + 4 * (self.FLAG_FLOATS + d * self.n)
+
+    def flag_ptr(self, rank: int, d: int, ack: bool) -> int:
+        return self.ptrs[rank] + 16 * d + (8 if ack else 0)
+
+    @classmethod
+    def get(cls, group, numel: int, device):
+        """The link of this group for states of ``numel`` floats, built on first use (a collective: every rank of
+        the group comes here in the same call).  ``None`` when the ranks are not on one node or the mapping cannot
+        be set up; all ranks then agree on that and use send / recv."""
+        key = (id(group) if group is not None else 0, int(numel))
+        if key not in cls._links:
+            cls._links[key] = cls._build(group, numel, device)
+        return cls._links[key]
+
+    @classmethod
+    def _build(cls, group, numel, device):
+        import socket
+
+        def all_agree(ok: bool) -> bool:
+            t = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+            return bool(t.item())
+
+        world = dist.get_world_size(group)
+        names = [None] * world
+        dist.all_gather_object(names, socket.gethostname(), group=group)
+        ok = len(set(names)) == 1 and dist.get_backend(group) == "nccl"
+        try:
+            import torch.distributed._symmetric_memory  # noqa: F401
+        except Exception:                                   # noqa: BLE001
+            ok = False
+        if not all_agree(ok):
+            return None
+        link = None
+        try:
+            link = cls(group, numel, device)
+        except Exception:                                   # noqa: BLE001  (no peer access, old driver, ...)
+            link = None
+        if not all_agree(link is not None):
+            return None
+        dist.barrier(group)                                 # every rank's flags are zero before anybody signals
+        return link
+
+
+def chain_peer(link: PeerLink, d: int, rank: int, world: int, local, stream) -> None:
+    """One hop of direction ``d`` (0: down, 1: up) over a :class:`PeerLink`.  ``local(inc, out_ptr)`` enqueues the
+    boundary scan: ``inc`` is the incoming state (a view of this rank's inbox, ``None`` at the start of the chain)
+    and ``out_ptr`` the address in the NEXT rank's inbox where the outgoing state goes (``None`` at the end)."""
+    lib = L.lib()
+    src, dst = (rank - 1, rank + 1) if d == 0 else (rank + 1, rank - 1)
+    has_src, has_dst = 0 <= src < world, 0 <= dst < world
+    link.epoch[d] += 1
+    e = link.epoch[d]
+    inc = out_ptr = None
+    if has_src:
+        inbox = link.inbox(d)
+        L.check(lib.palimpsa_peer_wait(link.flag_ptr(rank, d, False), e, link.timeout_ms, inbox.data_ptr(), stream),
+                "wait for the previous rank's boundary state")
+        inc = inbox
+    if has_dst:
+        L.check(lib.palimpsa_peer_wait(link.flag_ptr(rank, d, True), e - 1, link.timeout_ms, None, stream),
+                "wait for the next rank to have read the previous state")
+        out_ptr = link.inbox_ptr(dst, d)
+    local(inc, out_ptr)
+    if has_dst:
+        L.check(lib.palimpsa_peer_signal(link.flag_ptr(dst, d, False), e, stream), "publish the boundary state")
+    if has_src:
+        L.check(lib.palimpsa_peer_signal(link.flag_ptr(src, d, True), e, stream), "release the previous rank's buffer")
+
+
 # --------------------------------------------------------------------------------------------------
 # CUDA backend of the context-parallel op
 # --------------------------------------------------------------------------------------------------
@@ -118,11 +228,21 @@ class _CudaLocal:
     def summary(self):
         L.check(self.lib.palimpsa_segment_summary(C.byref(self.prob), C.byref(self.sg), self.stream), "segment summary")
 
-    def combine(self, inc):
-        out = self.state_like()
-        a, bb = (None, None) if inc is None else (inc[0].data_ptr(), inc[1].data_ptr())
-        L.check(self.lib.palimpsa_cp_combine(C.byref(self.prob), C.byref(self.sg), a, bb, out[0].data_ptr(),
-                                             out[1].data_ptr(), self.stream), "boundary scan")
+    def _halves(self, inc, out_ptr):
+        """(in_M, in_J, out_M, out_J, out tensor): ``inc`` a [2,N,H,V,KP] tensor (or its flat view) or None;
+        ``out_ptr`` a raw address to write the outgoing pair to (a peer's inbox) or None for a fresh local tensor."""
+        half = 4 * self.N * self.H * self.V * self.KP
+        a, bb = (None, None) if inc is None else (inc.data_ptr(), inc.data_ptr() + half)
+        out = None
+        if out_ptr is None:
+            out = self.state_like()
+            out_ptr = out.data_ptr()
+        return a, bb, out_ptr, out_ptr + half, out
+
+    def combine(self, inc, out_ptr=None):
+        a, bb, om, oj, out = self._halves(inc, out_ptr)
+        L.check(self.lib.palimpsa_cp_combine(C.byref(self.prob), C.byref(self.sg), a, bb, om, oj, self.stream),
+                "boundary scan")
         return out
 
     def forward(self, save_ckpt: bool):
@@ -170,11 +290,10 @@ class _CudaLocal:
         prm = self._bwd_params(do, ckM, ckI)
         L.check(self.lib.palimpsa_chunk_bwd_segments(C.byref(prm), C.byref(sg), 1, self.stream), "backward carry pass")
 
-    def combine_bwd(self, sg, inc):
-        out = self.state_like()
-        a, bb = (None, None) if inc is None else (inc[0].data_ptr(), inc[1].data_ptr())
-        L.check(self.lib.palimpsa_cp_combine_bwd(C.byref(self.prob), C.byref(sg), a, bb, out[0].data_ptr(),
-                                                 out[1].data_ptr(), self.stream), "boundary scan (backward)")
+    def combine_bwd(self, sg, inc, out_ptr=None):
+        a, bb, om, oi, out = self._halves(inc, out_ptr)
+        L.check(self.lib.palimpsa_cp_combine_bwd(C.byref(self.prob), C.byref(sg), a, bb, om, oi, self.stream),
+                "boundary scan (backward)")
         return out
 
     def _outs(self, do, ckM, ckI):
@@ -213,16 +332,19 @@ class _CudaLocal:
 class _CpChunkPalimpsa(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, b, gt, g, Ip, scale, group, num_segments, reduce_param_grads, init_mu, init_I,
-                uncertainty):
+                uncertainty, link):
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         loc = _CudaLocal(q, k, v, b, gt, g, Ip, scale, num_segments, first_rank=(rank == 0), init_mu=init_mu,
                          init_I=init_I, uncertainty=uncertainty)
         need_grad = any(ctx.needs_input_grad[:7])
         with torch.cuda.device(q.device):
             loc.summary()                                    # no dependence on other ranks
-            chain_down(rank, world, group, loc.combine, loc.state_like())
+            if link is not None:
+                chain_peer(link, 0, rank, world, loc.combine, loc.stream)
+            else:
+                chain_down(rank, world, group, loc.combine, loc.state_like())
             o, o_var, fmu, fI, ckM, ckI = loc.forward(save_ckpt=need_grad)
-        ctx.loc, ctx.group, ctx.reduce = loc, group, reduce_param_grads
+        ctx.loc, ctx.group, ctx.reduce, ctx.link = loc, group, reduce_param_grads, link
         ctx.set_materialize_grads(False)                 # no zero tensors for outputs that received no gradient
         ctx.rank, ctx.world = rank, world
         if need_grad:
@@ -249,33 +371,43 @@ class _CpChunkPalimpsa(torch.autograd.Function):
             loc.do_var = torch.zeros_like(do) if do_var is None else do_var.to(io).contiguous()
         with torch.cuda.device(do.device):
             sg, bufs = loc.bwd_segments(decay)
+
+            def hop_up():
+                if ctx.link is not None:
+                    chain_peer(ctx.link, 1, ctx.rank, ctx.world, lambda inc, out: loc.combine_bwd(sg, inc, out),
+                               loc.stream)
+                else:
+                    chain_up(ctx.rank, ctx.world, ctx.group, lambda inc: loc.combine_bwd(sg, inc), loc.state_like())
+
             if loc.tensor_core_carry():
                 # the heavy pass needs no remote data: it runs BEFORE the chain, on all ranks at once
                 outs, ws, prm = loc.backward_main(do, ckM, ckI, sg)
-                chain_up(ctx.rank, ctx.world, ctx.group, lambda inc: loc.combine_bwd(sg, inc), loc.state_like())
+                hop_up()
                 loc.backward_finish(prm, sg)
                 dq, dk, dv, db, dgt, dg, dIp = outs
             else:
                 loc.bwd_carry(do, ckM, ckI, sg)              # zero-carry state gradients of every segment
-                chain_up(ctx.rank, ctx.world, ctx.group, lambda inc: loc.combine_bwd(sg, inc), loc.state_like())
+                hop_up()
                 dq, dk, dv, db, dgt, dg, dIp = loc.backward(do, ckM, ckI, sg)
             if ctx.reduce and ctx.world > 1:
                 pg = torch.stack([dg, dIp])
                 dist.all_reduce(pg, group=ctx.group)
                 dg, dIp = pg[0], pg[1]
-        return dq, dk, dv, db, dgt, dg, dIp, None, None, None, None, None, None, None
+        return dq, dk, dv, db, dgt, dg, dIp, None, None, None, None, None, None, None, None
 
 
 def cp_chunk_palimpsa(q, k, v, b, gt, g, Ip, group=None, scale=None, output_final_state=False, num_segments=None,
                       reduce_param_grads=True, initial_mu_state=None, initial_I_state=None,
-                      output_uncertainty=False):
+                      output_uncertainty=False, transport: str = "auto"):
     """Context-parallel ``chunk_palimpsa``: every rank of ``group`` passes ITS contiguous share of the
     sequence (``q,k [B,T_local,H,K]`` ...; shares in rank order; lengths may differ) and gets its share of
     ``o`` and of the gradients.  With ``output_final_state`` also returns the state after this rank's
     last token (the sequence's final state on the last rank).  ``dg`` / ``dIp`` are summed over the group
     unless ``reduce_param_grads=False``.  ``initial_mu_state`` / ``initial_I_state`` ``[B,H,V,K]`` (both or
     neither) are the state before the sequence's first token: only the first rank's are used, and they get
-    no gradient, as in ``chunk_palimpsa``.  ``output_uncertainty`` returns ``(o, o_var)`` in place of ``o``."""
+    no gradient, as in ``chunk_palimpsa``.  ``output_uncertainty`` returns ``(o, o_var)`` in place of ``o``.
+    ``transport``: ``"nccl"`` (send / recv), ``"peer"`` (stores into the next rank's mapped buffer, :class:`PeerLink`;
+    an error if it cannot be set up) or ``"auto"`` (peer where available, else nccl); the same on every rank."""
     from .ops.palimpsa import _core
     _core._require_cuda(q, k, v, b, gt, g, Ip)
     if scale is None:
@@ -296,8 +428,16 @@ def cp_chunk_palimpsa(q, k, v, b, gt, g, Ip, group=None, scale=None, output_fina
             raise ValueError(f"initial states must have shape {shape}")
         initial_mu_state = initial_mu_state.detach().float().contiguous()
         initial_I_state = initial_I_state.detach().float().contiguous()
+    if transport not in ("auto", "nccl", "peer"):
+        raise ValueError(f"transport must be 'auto', 'nccl' or 'peer', got {transport!r}")
+    link = None
+    if transport != "nccl" and dist.get_world_size(group) > 1:
+        link = PeerLink.get(group, 2 * B * H * v.shape[-1] * _core.padded_k(K), q.device)
+        if link is None and transport == "peer":
+            raise RuntimeError("palimpsa_b200: the ranks' buffers cannot be mapped into each other's address space "
+                               "(not one node, no peer access, or no symmetric-memory support); use transport='nccl'")
     o, o_var, fmu, fI = _CpChunkPalimpsa.apply(q, k, v, b, gt, g, Ip, float(scale), group, int(num_segments),
                                                bool(reduce_param_grads), initial_mu_state, initial_I_state,
-                                               bool(output_uncertainty))
+                                               bool(output_uncertainty), link)
     out = (o, o_var) if output_uncertainty else o
     return (out, fmu, fI) if output_final_state else out

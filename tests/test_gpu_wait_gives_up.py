@@ -39,3 +39,28 @@ def test_bounded_wait_runs_out_and_the_device_stays_usable():
     compare(run_cuda(inp, "chunk"), run_oracle(inp), TOL_FP32, what="after the probe")
     from palimpsa_b200 import _lib
     assert _lib.lib().palimpsa_tensor_core_status() == 0     # the probe's own status word is not the library's
+
+
+def test_peer_wait_runs_out_records_its_code_and_poisons_the_buffer():
+    """The stream-ordered wait on a peer's flag (used by the context-parallel hops) on ONE GPU: a flag nobody sets
+    makes it run out after its wall-clock limit (5 ms here); it records code 7, writes a NaN into the buffer it
+    guards and lets the stream go on.  After a signal the same wait passes."""
+    from palimpsa_b200 import _lib
+    lib = _lib.lib()
+    lib.palimpsa_tensor_core_status()                                   # clear whatever earlier tests left
+    flag = torch.zeros(1, dtype=torch.int64, device="cuda:0")
+    guarded = torch.ones(4, dtype=torch.float32, device="cuda:0")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.palimpsa_peer_wait(flag.data_ptr(), 1, 5, guarded.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert lib.palimpsa_tensor_core_status() == 7
+    assert torch.isnan(guarded[0]) and bool((guarded[1:] == 1).all())
+    assert lib.palimpsa_tensor_core_status() == 0                       # reading cleared it
+    guarded.fill_(1.0)
+    assert lib.palimpsa_peer_signal(flag.data_ptr(), 3, stream) == 0    # sequence numbers only grow: 3 >= 1 and >= 2
+    assert lib.palimpsa_peer_wait(flag.data_ptr(), 1, 5, guarded.data_ptr(), stream) == 0
+    assert lib.palimpsa_peer_wait(flag.data_ptr(), 2, 5, guarded.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert flag.item() == 3 and lib.palimpsa_tensor_core_status() == 0 and bool((guarded == 1).all())
+    assert lib.palimpsa_peer_wait(None, 1, 5, None, stream) == _lib.E_NULL
+    assert lib.palimpsa_peer_signal(flag.data_ptr() + 4, 1, stream) == _lib.E_ALIGN   # flags are 8-byte aligned
