@@ -37,7 +37,7 @@
 extern "C" {
 #endif
 
-#define PALIMPSA_ABI_VERSION 10
+#define PALIMPSA_ABI_VERSION 11
 
 /* io dtype of q, k, v, b, o, o_var, do, do_var, dq, dk, dv, db */
 #define PALIMPSA_F32 0
@@ -169,6 +169,19 @@ int palimpsa_cp_combine(const palimpsa_problem *p, const palimpsa_segments *segs
  * (out_M, out_I), if given, receive dL/d(start state of segment 0). */
 int palimpsa_cp_combine_bwd(const palimpsa_problem *p, const palimpsa_segments *segs, const float *in_M,
                             const float *in_I, float *out_M, float *out_I, void *cuda_stream);
+
+/* A rank in the middle of a context-parallel chain, split so that only three state-sized streams lie between the
+ * arrival of a boundary state and its departure.  palimpsa_cp_relay_prepare, enqueued BEFORE the state arrives,
+ * computes what the rank's own segments add to a state that passes through ([N,H,V,KP] pairs, float32): forward
+ * (backward = 0) the end state of its segments from a zero start, out of sum_M/sum_J and decay; backward
+ * (backward = 1) the start-state gradient from a zero end-state gradient, out of rloc_M/rloc_I and decay.
+ * palimpsa_cp_relay then forms  out = (product of the segments' decays) * in + total.  The full boundary scan
+ * (palimpsa_cp_combine[_bwd] with the same `in`) follows off the chain's critical path.  Same algebra as the scan
+ * (the recurrence is linear in the state with a scalar decay per head); no counterpart in the reference. */
+int palimpsa_cp_relay_prepare(const palimpsa_problem *p, const palimpsa_segments *segs, int backward, float *tot_A,
+                              float *tot_B, void *cuda_stream);
+int palimpsa_cp_relay(const palimpsa_problem *p, const palimpsa_segments *segs, const float *in_A, const float *in_B,
+                      const float *tot_A, const float *tot_B, float *out_A, float *out_B, void *cuda_stream);
 
 /* Hand-over of a boundary state between the GPUs of one node without a host round trip or a library call per hop.
  * The exchange buffers of the ranks are mapped into each other's address space (CUDA peer / symmetric memory: the

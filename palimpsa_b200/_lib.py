@@ -7,7 +7,7 @@ import os
 PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libpalimpsa_b200.so")
 
-ABI_VERSION = 10
+ABI_VERSION = 11
 F32, BF16, F16 = 0, 1, 2
 FLAG_UNCERTAINTY = 1
 FLAG_EXPLICIT_INIT = 2
@@ -106,6 +106,10 @@ SYMBOLS = {
                                       C.c_void_p, C.c_void_p]),
     "palimpsa_cp_combine_bwd": (C.c_int, [C.POINTER(Problem), C.POINTER(Segments), C.c_void_p, C.c_void_p, C.c_void_p,
                                           C.c_void_p, C.c_void_p]),
+    "palimpsa_cp_relay_prepare": (C.c_int, [C.POINTER(Problem), C.POINTER(Segments), C.c_int, C.c_void_p, C.c_void_p,
+                                            C.c_void_p]),
+    "palimpsa_cp_relay": (C.c_int, [C.POINTER(Problem), C.POINTER(Segments), C.c_void_p, C.c_void_p, C.c_void_p,
+                                    C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "palimpsa_chunk_fwd_segments": (C.c_int, [C.POINTER(FwdParams), C.POINTER(Segments), C.c_void_p]),
     "palimpsa_chunk_bwd_segments": (C.c_int, [C.POINTER(BwdParams), C.POINTER(Segments), C.c_int, C.c_void_p]),
     "palimpsa_carry_apply_supported": (C.c_int, [C.POINTER(Problem)]),

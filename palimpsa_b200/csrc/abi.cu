@@ -222,6 +222,32 @@ int palimpsa_cp_combine_bwd(const palimpsa_problem* p, const palimpsa_segments* 
     return launch_combine_bwd(*p, *sg, in_M, in_I, out_M, out_I, static_cast<cudaStream_t>(cuda_stream));
 }
 
+int palimpsa_cp_relay_prepare(const palimpsa_problem* p, const palimpsa_segments* sg, int backward, float* tot_A,
+                              float* tot_B, void* cuda_stream) {
+    if (!p || !tot_A || !tot_B) return PALIMPSA_E_NULL;
+    int rc = check_problem(*p);
+    if (rc) return rc;
+    rc = check_segments(*p, sg);
+    if (rc) return rc;
+    if (!sg->decay || (backward ? (!sg->rloc_M || !sg->rloc_I) : (!sg->sum_M || !sg->sum_J))) return PALIMPSA_E_NULL;
+    if (misaligned16(tot_A) || misaligned16(tot_B)) return PALIMPSA_E_ALIGN;
+    return launch_relay_total(*p, *sg, backward ? 1 : 0, tot_A, tot_B, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int palimpsa_cp_relay(const palimpsa_problem* p, const palimpsa_segments* sg, const float* in_A, const float* in_B,
+                      const float* tot_A, const float* tot_B, float* out_A, float* out_B, void* cuda_stream) {
+    if (!p || !in_A || !in_B || !tot_A || !tot_B || !out_A || !out_B) return PALIMPSA_E_NULL;
+    int rc = check_problem(*p);
+    if (rc) return rc;
+    rc = check_segments(*p, sg);
+    if (rc) return rc;
+    if (!sg->decay) return PALIMPSA_E_NULL;
+    if (misaligned16(in_A) || misaligned16(in_B) || misaligned16(tot_A) || misaligned16(tot_B) || misaligned16(out_A) ||
+        misaligned16(out_B))
+        return PALIMPSA_E_ALIGN;
+    return launch_relay(*p, *sg, in_A, in_B, tot_A, tot_B, out_A, out_B, static_cast<cudaStream_t>(cuda_stream));
+}
+
 int palimpsa_chunk_fwd_segments(const palimpsa_fwd_params* prm, const palimpsa_segments* sg, void* cuda_stream) {
     int rc = check_fwd(prm);
     if (rc) return rc;

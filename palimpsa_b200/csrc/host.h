@@ -43,6 +43,13 @@ int launch_peer_wait(const void* flag, unsigned long long value, unsigned timeou
 int launch_peer_signal(void* flag, unsigned long long value, cudaStream_t stream);
 int peer_status();   // 0, or 7 when a wait ran out
 
+// A context-parallel hop split in two (segments.cu): what this rank adds to a state passing through, computed
+// before the state arrives, and out = decay_product * in + total when it does.
+int launch_relay_total(const palimpsa_problem& p, const palimpsa_segments& segs, int backward, float* tot_A,
+                       float* tot_B, cudaStream_t stream);
+int launch_relay(const palimpsa_problem& p, const palimpsa_segments& segs, const float* in_A, const float* in_B,
+                 const float* tot_A, const float* tot_B, float* out_A, float* out_B, cudaStream_t stream);
+
 // Backward whose scratch is the library's own fixed device array (bwd.cu).
 int launch_bwd_static(const palimpsa_bwd_params* prm, cudaStream_t stream);
 

@@ -167,16 +167,21 @@ class PeerLink:
         return link
 
 
-def chain_peer(link: PeerLink, d: int, rank: int, world: int, local, stream) -> None:
-    """One hop of direction ``d`` (0: down, 1: up) over a :class:`PeerLink`.  ``local(inc, out_ptr)`` enqueues the
-    boundary scan: ``inc`` is the incoming state (a view of this rank's inbox, ``None`` at the start of the chain)
-    and ``out_ptr`` the address in the NEXT rank's inbox where the outgoing state goes (``None`` at the end)."""
+def chain_peer(link: PeerLink, d: int, rank: int, world: int, local, stream, prepare=None, relay=None) -> None:
+    """One hop of direction ``d`` (0: down, 1: up) over a :class:`PeerLink`.  ``local(inc, out_ptr, want_out)``
+    enqueues the boundary scan: ``inc`` is the incoming state (a view of this rank's inbox, ``None`` at the start of
+    the chain) and ``out_ptr`` the address in the NEXT rank's inbox where the outgoing state goes (``None`` at the
+    end).  A rank in the middle shortens the chain's critical path with ``prepare() -> total`` (enqueued before the
+    wait: what its own segments add, independent of the incoming state) and ``relay(inc, total, out_ptr)``
+    (``out = decay * inc + total``): the next rank is signalled right after the relay, the full scan follows."""
     lib = L.lib()
     src, dst = (rank - 1, rank + 1) if d == 0 else (rank + 1, rank - 1)
     has_src, has_dst = 0 <= src < world, 0 <= dst < world
     link.epoch[d] += 1
     e = link.epoch[d]
     inc = out_ptr = None
+    middle = has_src and has_dst and prepare is not None and relay is not None
+    total = prepare() if middle else None
     if has_src:
         inbox = link.inbox(d)
         L.check(lib.palimpsa_peer_wait(link.flag_ptr(rank, d, False), e, link.timeout_ms, inbox.data_ptr(), stream),
@@ -186,9 +191,14 @@ def chain_peer(link: PeerLink, d: int, rank: int, world: int, local, stream) -> 
         L.check(lib.palimpsa_peer_wait(link.flag_ptr(rank, d, True), e - 1, link.timeout_ms, None, stream),
                 "wait for the next rank to have read the previous state")
         out_ptr = link.inbox_ptr(dst, d)
-    local(inc, out_ptr)
-    if has_dst:
+    if middle:
+        relay(inc, total, out_ptr)
         L.check(lib.palimpsa_peer_signal(link.flag_ptr(dst, d, False), e, stream), "publish the boundary state")
+        local(inc, None, False)
+    else:
+        local(inc, out_ptr, has_dst)
+        if has_dst:
+            L.check(lib.palimpsa_peer_signal(link.flag_ptr(dst, d, False), e, stream), "publish the boundary state")
     if has_src:
         L.check(lib.palimpsa_peer_signal(link.flag_ptr(src, d, True), e, stream), "release the previous rank's buffer")
 
@@ -228,19 +238,33 @@ class _CudaLocal:
     def summary(self):
         L.check(self.lib.palimpsa_segment_summary(C.byref(self.prob), C.byref(self.sg), self.stream), "segment summary")
 
-    def _halves(self, inc, out_ptr):
+    def _halves(self, inc, out_ptr, want_out=True):
         """(in_M, in_J, out_M, out_J, out tensor): ``inc`` a [2,N,H,V,KP] tensor (or its flat view) or None;
-        ``out_ptr`` a raw address to write the outgoing pair to (a peer's inbox) or None for a fresh local tensor."""
+        ``out_ptr`` a raw address to write the outgoing pair to (a peer's inbox) or None for a fresh local tensor;
+        ``want_out=False``: the scan writes no outgoing state at all."""
         half = 4 * self.N * self.H * self.V * self.KP
         a, bb = (None, None) if inc is None else (inc.data_ptr(), inc.data_ptr() + half)
+        if not want_out:
+            return a, bb, None, None, None
         out = None
         if out_ptr is None:
             out = self.state_like()
             out_ptr = out.data_ptr()
         return a, bb, out_ptr, out_ptr + half, out
 
-    def combine(self, inc, out_ptr=None):
-        a, bb, om, oj, out = self._halves(inc, out_ptr)
+    def relay_prepare(self, sg, backward: bool):
+        tot = self.state_like()
+        L.check(self.lib.palimpsa_cp_relay_prepare(C.byref(self.prob), C.byref(sg), int(backward), tot[0].data_ptr(),
+                                                   tot[1].data_ptr(), self.stream), "relay total")
+        return tot
+
+    def relay(self, sg, inc, tot, out_ptr):
+        a, bb, oa, ob, _ = self._halves(inc, out_ptr)
+        L.check(self.lib.palimpsa_cp_relay(C.byref(self.prob), C.byref(sg), a, bb, tot[0].data_ptr(), tot[1].data_ptr(),
+                                           oa, ob, self.stream), "relay")
+
+    def combine(self, inc, out_ptr=None, want_out=True):
+        a, bb, om, oj, out = self._halves(inc, out_ptr, want_out)
         L.check(self.lib.palimpsa_cp_combine(C.byref(self.prob), C.byref(self.sg), a, bb, om, oj, self.stream),
                 "boundary scan")
         return out
@@ -290,8 +314,8 @@ class _CudaLocal:
         prm = self._bwd_params(do, ckM, ckI)
         L.check(self.lib.palimpsa_chunk_bwd_segments(C.byref(prm), C.byref(sg), 1, self.stream), "backward carry pass")
 
-    def combine_bwd(self, sg, inc, out_ptr=None):
-        a, bb, om, oi, out = self._halves(inc, out_ptr)
+    def combine_bwd(self, sg, inc, out_ptr=None, want_out=True):
+        a, bb, om, oi, out = self._halves(inc, out_ptr, want_out)
         L.check(self.lib.palimpsa_cp_combine_bwd(C.byref(self.prob), C.byref(sg), a, bb, om, oi, self.stream),
                 "boundary scan (backward)")
         return out
@@ -340,7 +364,9 @@ class _CpChunkPalimpsa(torch.autograd.Function):
         with torch.cuda.device(q.device):
             loc.summary()                                    # no dependence on other ranks
             if link is not None:
-                chain_peer(link, 0, rank, world, loc.combine, loc.stream)
+                chain_peer(link, 0, rank, world, loc.combine, loc.stream,
+                           prepare=lambda: loc.relay_prepare(loc.sg, False),
+                           relay=lambda inc, tot, out: loc.relay(loc.sg, inc, tot, out))
             else:
                 chain_down(rank, world, group, loc.combine, loc.state_like())
             o, o_var, fmu, fI, ckM, ckI = loc.forward(save_ckpt=need_grad)
@@ -374,8 +400,10 @@ class _CpChunkPalimpsa(torch.autograd.Function):
 
             def hop_up():
                 if ctx.link is not None:
-                    chain_peer(ctx.link, 1, ctx.rank, ctx.world, lambda inc, out: loc.combine_bwd(sg, inc, out),
-                               loc.stream)
+                    chain_peer(ctx.link, 1, ctx.rank, ctx.world,
+                               lambda inc, out, want: loc.combine_bwd(sg, inc, out, want), loc.stream,
+                               prepare=lambda: loc.relay_prepare(sg, True),
+                               relay=lambda inc, tot, out: loc.relay(sg, inc, tot, out))
                 else:
                     chain_up(ctx.rank, ctx.world, ctx.group, lambda inc: loc.combine_bwd(sg, inc), loc.state_like())
 

@@ -121,3 +121,35 @@ def test_tensor_core_carry_other_shapes(K, V, T, G):
     got = _run(inp, G)
     ref = run_oracle(inp)
     compare(got, ref, TOL_BF16, what=f"tensor-core carry K={K} V={V}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_relay_of_a_passing_state_equals_the_full_boundary_scan(dtype):
+    """A rank in the middle of a context-parallel chain forwards ``decay * in + total`` (total computed before the
+    state arrives) instead of waiting for its full boundary scan: both must give the same outgoing state, forward
+    (boundary state) and backward (state gradient).  One GPU: the rank's local machinery needs no process group."""
+    from palimpsa_b200.parallel import _CudaLocal
+    inp = orc.make_inputs(41, B=2, T=700, H=3, K=64, V=48, dtype=dtype)
+    inp["gt"] = inp["gt"] * 0.05
+    t = [inp[n].to(DEV).contiguous() for n in ("q", "k", "v", "b", "gt", "g", "Ip")]
+    loc = _CudaLocal(*t, 64 ** -0.5, 5, first_rank=False)
+    gen = torch.Generator().manual_seed(7)
+    loc.summary()
+    inc = torch.randn(loc.state_like().shape, generator=gen).to(DEV)
+    full = loc.combine(inc)
+    tot = loc.relay_prepare(loc.sg, False)
+    out = torch.full_like(full, float("nan"))
+    loc.relay(loc.sg, inc, tot, out.data_ptr())
+    torch.cuda.synchronize()
+    assert orc.rel_err(out, full) <= 2e-6
+    # backward: start-state gradients of the segments from a zero end-state gradient, then the two routes
+    o, _, _, _, ckM, ckI = loc.forward(save_ckpt=True)
+    sg, bufs = loc.bwd_segments(loc.bufs["decay"])
+    loc.bwd_carry(inp["do"].to(DEV).to(o.dtype).contiguous(), ckM, ckI, sg)
+    inc = torch.randn(loc.state_like().shape, generator=gen).to(DEV)
+    full = loc.combine_bwd(sg, inc)
+    tot = loc.relay_prepare(sg, True)
+    out = torch.full_like(full, float("nan"))
+    loc.relay(sg, inc, tot, out.data_ptr())
+    torch.cuda.synchronize()
+    assert orc.rel_err(out, full) <= 2e-6
