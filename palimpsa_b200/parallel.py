@@ -105,6 +105,10 @@ class PeerLink:
     _links = {}                                             # (group id, numel) -> PeerLink, or None if unavailable
 
     def __init__(self, group, numel: int, device, timeout_ms: int = 20000):
+        import os
+        # Only plain peer loads and stores are used here: ask torch not to bind the buffers to an NVLink multicast
+        # object as well (it reads the variable when its symmetric-memory code is first used).
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
         self.n, self.timeout_ms = int(numel), int(timeout_ms)
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
