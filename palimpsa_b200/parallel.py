@@ -99,7 +99,8 @@ class PeerLink:
     sequence number of the call in the consumer's ``ready`` flag; the consumer, once its kernels have read the inbox,
     publishes the same number in the producer's ``ack`` flag, and the producer waits for the previous number there
     before it overwrites the inbox.  Sequence numbers only grow, so nothing is ever reset.  Every rank must make the
-    same sequence of calls (as with any collective).  All waits are the library's bounded ones."""
+    same sequence of calls (as with any collective), and a rank must enqueue the calls of one group on one stream
+    (the hand-over is ordered by stream order).  All waits are the library's bounded ones."""
 
     FLAG_FLOATS = 16                                        # 64 bytes of flags in front of the inboxes
     _links = {}                                             # (group id, numel) -> PeerLink, or None if unavailable
@@ -136,7 +137,8 @@ class PeerLink:
         """The link of this group for states of ``numel`` floats, built on first use (a collective: every rank of
         the group comes here in the same call).  ``None`` when the ranks are not on one node or the mapping cannot
         be set up; all ranks then agree on that and use send / recv."""
-        key = (id(group) if group is not None else 0, int(numel))
+        pg = group if group is not None else dist.group.WORLD
+        key = (getattr(pg, "group_name", None) or id(pg), int(numel))
         if key not in cls._links:
             cls._links[key] = cls._build(group, numel, device)
         return cls._links[key]
