@@ -23,7 +23,7 @@ the metric in the same line:
     decode     256 sequences x 12 heads, fp32 (mu, I) cache, single-token bf16 steps: tokens/s and HBM GB/s
     varlen     one packed batch of 32 768 tokens, documents of seeded random length in [128, 4096]
     c5         one 131 072-token sequence, H=12: one GPU with the planner's segments (N=1), or context-parallel
-               over the N ranks (boundary states by NCCL send/recv), with the one-GPU time measured in the same run
+               over the N ranks (boundary states through peer-mapped buffers, and by NCCL send/recv beside it), with the one-GPU time measured in the same run
     c2_strong  the C2 batch (global B=8) sharded over the N ranks by (sequence, head): strong scaling
 
 ``--impl reference`` times only the CPU recurrence (the reference has no other CPU path).
@@ -636,7 +636,7 @@ def model_shapes_workload(dev, steps, with_reference):
 def c5_workload(dev, rank, world, steps):
     """C5: one 131 072-token sequence, H=12, d_k=d_v=128, bf16 fwd+bwd.  N=1: the single-GPU op with the planner's
     segments.  N>=2: ``cp_chunk_palimpsa`` over the N ranks (each rank holds T/N contiguous tokens; boundary states
-    travel rank to rank by NCCL send/recv); rank 0 also times the whole sequence on its own GPU for the speed-up."""
+    travel rank to rank through peer-mapped buffers, and once more by NCCL send/recv for comparison); rank 0 also times the whole sequence on its own GPU for the speed-up."""
     from palimpsa_b200.ops.palimpsa._core import padded_k, plan_segments
     B, T, H, K, V = C5["B"], C5["T"], C5["H"], C5["K"], C5["V"]
     out = {"workload": f"C5 long context B={B} T={T} H={H} d_k={K} d_v={V} bf16 chunk fwd+bwd"}
@@ -682,8 +682,8 @@ def c5_workload(dev, rank, world, steps):
                ms_per_step_send_recv=ms_nccl,
                collective="one 1.5 MB boundary state per hop, down in forward and up in backward; all-reduce of dg, "
                           "dIp (2*H floats)",
-               limited_by="the rank-to-rank chain is serial: 2*(N-1) hops of one small message plus one boundary-scan "
-                          "kernel each; the heavy kernels run on all ranks side by side")
+               limited_by="the rank-to-rank chain is serial: 2*(N-1) hops of wait, relay kernel (decay * in + total) and "
+                          "signal; the heavy kernels run on all ranks side by side")
     if single_ms is not None:
         out["speedup_vs_single_gpu"] = single_ms / ms
         out["efficiency"] = single_ms / ms / world
