@@ -25,6 +25,7 @@ the metric in the same line:
     c5         one 131 072-token sequence, H=12: one GPU with the planner's segments (N=1), or context-parallel
                over the N ranks (boundary states through peer-mapped buffers, and by NCCL send/recv beside it), with the one-GPU time measured in the same run
     c2_strong  the C2 batch (global B=8) sharded over the N ranks by (sequence, head): strong scaling
+    model_shapes  chunk fwd+bwd at the head shapes of the reference's shipped model configurations, beside its Triton ops
 
 ``--impl reference`` times only the CPU recurrence (the reference has no other CPU path).
 """
