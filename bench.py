@@ -987,6 +987,9 @@ def main():
     ap.add_argument("--profile-batch", type=int, default=4, help="batch size of --profile-case")
     ap.add_argument("--profile-segments", type=int, default=1,
                     help="with --profile-case: run one 32768-token sequence (H=12) cut into this many segments")
+    ap.add_argument("--profile-heads", default=None, metavar="H,DK,DV",
+                    help="with --profile-case: head count and dimensions instead of the benchmark's 6,128,128 "
+                         "(e.g. 16,48,48: the reference's 170M configuration)")
     ap.add_argument("--profile-case", action="store_true",
                     help="run a few forward+backward steps of a half-size batch (B=4) and exit: the small case "
                          "that profiler captures are taken on")
@@ -1001,7 +1004,8 @@ def main():
             torch.cuda.synchronize()
             print("profile case (segments) done")
             return
-        _, d = make_inputs(args.profile_batch, C2["T"], C2["H"], C2["K"], C2["V"], torch.bfloat16, dev)
+        H, K, V = [int(x) for x in args.profile_heads.split(",")] if args.profile_heads else (C2["H"], C2["K"], C2["V"])
+        _, d = make_inputs(args.profile_batch, C2["T"], H, K, V, torch.bfloat16, dev)
         for _ in range(3):
             fwd_bwd(d)
         torch.cuda.synchronize()
