@@ -155,7 +155,7 @@ class PeerLink:
         world = dist.get_world_size(group)
         names = [None] * world
         dist.all_gather_object(names, socket.gethostname(), group=group)
-        ok = len(set(names)) == 1 and dist.get_backend(group) == "nccl"
+        ok = len(set(names)) == 1 and "nccl" in str(dist.get_backend(group))
         try:
             import torch.distributed._symmetric_memory  # noqa: F401
         except Exception:                                   # noqa: BLE001
@@ -466,7 +466,8 @@ def cp_chunk_palimpsa(q, k, v, b, gt, g, Ip, group=None, scale=None, output_fina
         raise ValueError(f"transport must be 'auto', 'nccl' or 'peer', got {transport!r}")
     link = None
     if transport != "nccl" and dist.get_world_size(group) > 1:
-        link = PeerLink.get(group, 2 * B * H * v.shape[-1] * _core.padded_k(K), q.device)
+        with torch.cuda.device(q.device):                  # the set-up's collectives run on this rank's GPU
+            link = PeerLink.get(group, 2 * B * H * v.shape[-1] * _core.padded_k(K), q.device)
         if link is None and transport == "peer":
             raise RuntimeError("palimpsa_b200: the ranks' buffers cannot be mapped into each other's address space "
                                "(not one node, no peer access, or no symmetric-memory support); use transport='nccl'")
