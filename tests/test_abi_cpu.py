@@ -88,6 +88,20 @@ def test_validation_codes(L):
     assert lib.palimpsa_chunk_bwd(C.byref(b), None) == -2
 
 
+def test_peer_and_relay_entry_points_validate_before_any_launch(L):
+    """Argument checks of the multi-GPU hand-over entry points return their codes without touching a device."""
+    lib = L.lib()
+    assert lib.palimpsa_peer_wait(None, 1, 1, None, None) == L.E_NULL
+    assert lib.palimpsa_peer_signal(None, 1, None) == L.E_NULL
+    assert lib.palimpsa_peer_wait(0x1004, 1, 1, None, None) == L.E_ALIGN      # flags are 8-byte aligned
+    assert lib.palimpsa_peer_signal(0x1004, 1, None) == L.E_ALIGN
+    p, sg = L.Problem(), L.Segments()
+    assert lib.palimpsa_cp_relay_prepare(C.byref(p), C.byref(sg), 0, None, None, None) == L.E_NULL
+    assert lib.palimpsa_cp_relay(C.byref(p), C.byref(sg), None, None, None, None, None, None, None) == L.E_NULL
+    assert lib.palimpsa_cp_relay_prepare(C.byref(p), C.byref(sg), 0, 0x1000, 0x2000, None) == -2   # empty shapes
+    assert lib.palimpsa_bwd_tile_rows(128, 128, L.BF16, 0) == 22 and lib.palimpsa_bwd_tile_rows(0, 8, L.BF16, 0) == 0
+
+
 def test_python_wrappers_reject_cpu_tensors_and_bad_shapes():
     import torch
     from palimpsa_b200.ops import chunk_palimpsa, fused_recurrent_palimpsa
