@@ -209,3 +209,24 @@ def test_long_segmented_sequence_matches_the_float64_oracle():
     for lo, hi, tag in ((0, 2048, "first"), (32768 - 2048, 32768, "last")):
         win = {n: got[n][:, lo:hi] for n in ("o",) + PER_TOKEN}
         _check(win, {n: ref[n][:, lo:hi] for n in win}, tuple(win), f"{tag} 2048 tokens")
+
+
+def test_small_head_batch_matches_the_float64_oracle():
+    """The reference's 170M configuration (16 heads of d_k = d_v = 48) at the benchmark's length: B = 8, T = 4096,
+    bf16, through the 48-row tiles (3 forward / 6 backward warps per CTA).  One whole sequence: outputs and final
+    states on four heads, the per-token gradients on two; parameter gradients from a call on that slice alone."""
+    d = _inputs(8, 4096, 16, 48, 48)
+    a = _fwd_bwd(d)
+    seq = 3
+    sl = _cpu_slice(d, seq, slice(4, 8))
+    with torch.no_grad():
+        o, _, mu, I = orc.oracle_forward(*[sl[n] for n in NAMES])
+    got = {"o": a["o"][seq:seq + 1][:, :, 4:8], "mu": a["mu"][seq:seq + 1][:, 4:8], "I": a["I"][seq:seq + 1][:, 4:8]}
+    _check(got, {"o": o, "mu": mu, "I": I}, ("o", "mu", "I"), "170M heads, forward, heads 4-7")
+    heads = slice(9, 11)
+    sl2 = _cpu_slice(d, seq, heads)
+    ref = _explicit(sl2)
+    got = {n: a[n][seq:seq + 1][:, :, heads] for n in PER_TOKEN}
+    _check(got, ref, PER_TOKEN, "170M heads, gradients, heads 9-10")
+    alone = _fwd_bwd({n: x.to(DEV) for n, x in sl2.items()})
+    _check(alone, ref, ("dg", "dIp") + PER_TOKEN, "170M heads, slice alone (parameter gradients)")
